@@ -1,0 +1,315 @@
+// Packed-QKV padded bidirectional attention for sm_100a, head_dim 64.
+//
+// One CTA per (128-query tile, head, batch).  Q, K and V tiles are 128 x 64 fp16 boxes
+// that TMA lifts straight out of the packed [bs*seq, 3*heads*64] tensor into
+// 128-byte-swizzled shared memory.  S = Q.K^T (128 x 128, fp32) and O_j = P.V (128 x 64)
+// are tcgen05.mma results in tensor memory; the softmax runs one query row per thread in
+// fp32 with an online rescale across 128-wide KV tiles, so sequence lengths 128 and 512
+// share one code path and S / P never touch HBM.  KV tiles beyond a sequence's valid
+// length are skipped, the ragged tile is masked, and padded query rows are written as zeros.
+//
+// Replaces the reference's cuDNN fused attention behind TransformerEngine
+// (include/NVGPUKernels/BertAttentionRunner.h:52-136: layout BS3HD, no bias, padding mask,
+// no dropout, inference).
+#include "attention_sm100.cuh"
+#include "gemm_sm100.cuh"
+#include "ptx_sm100.cuh"
+
+namespace hom {
+namespace attention {
+
+using namespace hom::ptx;
+
+namespace {
+
+constexpr int kTile = 128;   // query rows per CTA and KV rows per step
+constexpr int kHeadDim = 64;
+constexpr int kThreads = 128;
+constexpr uint32_t kTileBytes = kTile * kHeadDim * 2;  // 16 KB
+constexpr uint32_t kSmemQ = 0;
+constexpr uint32_t kSmemK = kTileBytes;
+constexpr uint32_t kSmemV = 2 * kTileBytes;
+constexpr uint32_t kSmemP = 3 * kTileBytes;  // two 128 x 64 sub-tiles
+constexpr uint32_t kSmemBar = 5 * kTileBytes;
+constexpr uint32_t kSmemBytes = kSmemBar + 64 + 1024;
+constexpr uint32_t kTmemCols = 256;  // S: columns [0,128), O: columns [128,192)
+
+struct Params {
+  const int *cu_seqlens;  // [bs + 1]
+  __half *out;            // [bs*seq, heads*64]
+  int seq, heads;
+  float scale_log2;  // softmax scale * log2(e)
+  int *status;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int hidden = p.heads * kHeadDim;
+  const int q0 = q_tile * kTile;
+
+  int len = p.cu_seqlens[batch + 1] - p.cu_seqlens[batch];
+  len = max(0, min(len, p.seq));
+
+  const int q_idx = q0 + tid;
+  __half *out_row = p.out + (static_cast<long long>(batch) * p.seq + q_idx) * hidden + head * kHeadDim;
+
+  if (q0 >= len) {
+    // Entirely padded query tile.
+    if (q_idx < p.seq) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int g = 0; g < 8; ++g) reinterpret_cast<uint4 *>(out_row)[g] = z;
+    }
+    return;
+  }
+
+  const uint32_t bar_q = smem_base + kSmemBar;
+  const uint32_t bar_k = bar_q + 8, bar_v = bar_q + 16, bar_s = bar_q + 24, bar_o = bar_q + 32;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + 40);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_o = tmem_base + 128;
+  const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+
+  const int n_kv = (len + kTile - 1) / kTile;
+  const int row_base = batch * p.seq;
+  const int col_q = head * kHeadDim;
+  const int col_k = hidden + head * kHeadDim;
+  const int col_v = 2 * hidden + head * kHeadDim;
+
+  uint32_t armed_k = 0, armed_v = 0;  // thread 0 only
+  if (tid == 0) {
+    prefetch_tensormap(&tmQKV);
+    mbar_arrive_expect_tx(bar_q, kTileBytes);
+    tma_load_2d(smem_base + kSmemQ, &tmQKV, bar_q, col_q, row_base + q0);
+    mbar_arrive_expect_tx(bar_k, kTileBytes);
+    tma_load_2d(smem_base + kSmemK, &tmQKV, bar_k, col_k, row_base);
+    mbar_arrive_expect_tx(bar_v, kTileBytes);
+    tma_load_2d(smem_base + kSmemV, &tmQKV, bar_v, col_v, row_base);
+    armed_k = armed_v = 1;
+  }
+
+  constexpr uint32_t idesc_s = make_idesc_f16(kTile, kTile, false, false);
+  constexpr uint32_t idesc_o = make_idesc_f16(kTile, kHeadDim, false, true);
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float o_acc[kHeadDim];
+#pragma unroll
+  for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
+
+  bool ok = true;
+  for (int j = 0; j < n_kv && ok; ++j) {
+    const uint32_t ph = j & 1;
+    // ---- S = Q.K_j^T
+    if (tid == 0) {
+      bool w = true;
+      if (j == 0) w = mbar_wait(bar_q, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
+      w = w && mbar_wait(bar_k, ph, abort_flag, p.status, kDevWaitTimeoutAttention);
+      if (w) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < kHeadDim / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(smem_base + kSmemQ + k * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_base + kSmemK + k * 32, 16, 1024);
+          tc_mma_f16_ss(tmem_s, da, db, idesc_s, k != 0 ? 1u : 0u);
+        }
+        tc_commit(bar_s);
+      }
+    }
+    ok = mbar_wait(bar_s, ph, abort_flag, p.status, kDevWaitTimeoutAttention);
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tc_fence_after_sync();
+    if (tid == 0 && j + 1 < n_kv) {  // K buffer is free once S has been computed
+      mbar_arrive_expect_tx(bar_k, kTileBytes);
+      tma_load_2d(smem_base + kSmemK, &tmQKV, bar_k, col_k, row_base + (j + 1) * kTile);
+      ++armed_k;
+    }
+
+    // ---- softmax over this KV tile (one query row per thread)
+    const int kv0 = j * kTile;
+    const int valid = min(kTile, len - kv0);  // columns [0, valid) are real keys
+    float m_tile = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < kTile / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_s + lane_sel + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (c * 32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(r[i]) * p.scale_log2);
+    }
+    const float m_new = fmaxf(m_run, m_tile);
+    const float corr = exp2f(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+    float l_tile = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < kTile / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_s + lane_sel + c * 32, r);
+      tmem_ld_wait();
+      float pv[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float e = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_new));
+        pv[i] = (c * 32 + i < valid) ? e : 0.f;
+        l_tile += pv[i];
+      }
+      // P[row = tid][c*32 .. c*32+31] as fp16 into the K-major 128B-swizzled sub-tile.
+      const uint32_t sub = smem_base + kSmemP + (c >> 1) * kTileBytes + tid * 128;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t chunk = (c & 1) * 4 + g;
+        uint32_t w0, w1, w2, w3;
+        {
+          __half2 h;
+          h = __floats2half2_rn(pv[g * 8 + 0], pv[g * 8 + 1]);
+          w0 = *reinterpret_cast<uint32_t *>(&h);
+          h = __floats2half2_rn(pv[g * 8 + 2], pv[g * 8 + 3]);
+          w1 = *reinterpret_cast<uint32_t *>(&h);
+          h = __floats2half2_rn(pv[g * 8 + 4], pv[g * 8 + 5]);
+          w2 = *reinterpret_cast<uint32_t *>(&h);
+          h = __floats2half2_rn(pv[g * 8 + 6], pv[g * 8 + 7]);
+          w3 = *reinterpret_cast<uint32_t *>(&h);
+        }
+        const uint32_t addr = sub + ((chunk ^ (tid & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
+                     "r"(w2), "r"(w3)
+                     : "memory");
+      }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+
+    // ---- O_j = P.V_j
+    if (tid == 0) {
+      if (mbar_wait(bar_v, ph, abort_flag, p.status, kDevWaitTimeoutAttention)) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(
+              smem_base + kSmemP + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
+          // V tile: 128 kv rows of 128 B; N (= d) contiguous, 16 kv rows = 2048 B.
+          const uint64_t db = make_smem_desc_sw128(smem_base + kSmemV + k * 2048, kTileBytes, 1024);
+          tc_mma_f16_ss(tmem_o, da, db, idesc_o, k != 0 ? 1u : 0u);
+        }
+        tc_commit(bar_o);
+      }
+    }
+    ok = mbar_wait(bar_o, ph, abort_flag, p.status, kDevWaitTimeoutAttention);
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tc_fence_after_sync();
+    if (tid == 0 && j + 1 < n_kv) {  // V buffer is free once P.V has been computed
+      mbar_arrive_expect_tx(bar_v, kTileBytes);
+      tma_load_2d(smem_base + kSmemV, &tmQKV, bar_v, col_v, row_base + (j + 1) * kTile);
+      ++armed_v;
+    }
+#pragma unroll
+    for (int c = 0; c < kHeadDim / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_o + lane_sel + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], corr, __uint_as_float(r[i]));
+    }
+    l_run = fmaf(l_run, corr, l_tile);
+    m_run = m_new;
+  }
+
+  if (ok) {
+    if (q_idx < p.seq) {
+      const bool real_row = q_idx < len && l_run > 0.f;
+      const float inv = real_row ? 1.f / l_run : 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (real_row) {
+          __half2 *o2 = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            o2[jj] = __floats2half2_rn(o_acc[g * 8 + 2 * jj] * inv, o_acc[g * 8 + 2 * jj + 1] * inv);
+        }
+        reinterpret_cast<uint4 *>(out_row)[g] = o;
+      }
+    }
+  } else if (tid == 0) {
+    // Let copies that are still in flight land before the shared memory is released.
+    const long long t0 = clock64();
+    if (armed_k) while (!mbar_try_wait(bar_k, (armed_k - 1) & 1) && clock64() - t0 < 200000000LL) {}
+    if (armed_v) while (!mbar_try_wait(bar_v, (armed_v - 1) & 1) && clock64() - t0 < 400000000LL) {}
+    while (!mbar_try_wait(bar_q, 0) && clock64() - t0 < 600000000LL) {}
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+bool run(const Problem &pb, cudaStream_t stream) {
+  if (pb.bs == 0 || pb.seq == 0 || pb.heads == 0) return true;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (!check_cuda(cudaFuncSetAttribute(attention_f16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                    "cudaFuncSetAttribute(attention)"))
+      return false;
+    attr_set[dev] = true;
+  }
+  CUtensorMap tm;
+  const uint64_t rows = static_cast<uint64_t>(pb.bs) * pb.seq;
+  const uint64_t cols = 3ull * pb.heads * kHeadDim;
+  if (!gemm::make_tensor_map_2d(pb.qkv, cols, rows, kHeadDim, kTile, &tm)) return false;
+  Params p;
+  p.cu_seqlens = pb.cu_seqlens;
+  p.out = pb.out;
+  p.seq = static_cast<int>(pb.seq);
+  p.heads = static_cast<int>(pb.heads);
+  p.scale_log2 = pb.scale * 1.44269504088896340736f;
+  p.status = device_status_word();
+  dim3 grid(static_cast<unsigned>((pb.seq + kTile - 1) / kTile), static_cast<unsigned>(pb.heads),
+            static_cast<unsigned>(pb.bs));
+  const double d = kHeadDim;
+  const double flops = 4.0 * d * pb.heads * pb.bs * static_cast<double>(pb.seq) * pb.seq;
+  const double bytes = 2.0 * rows * cols + 2.0 * rows * pb.heads * d + 4.0 * (pb.bs + 1);
+  LaunchScope scope(kOpAttention, flops, bytes);
+  attention_f16_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm, p);
+  return check_cuda(cudaGetLastError(), "attention kernel launch");
+}
+
+}  // namespace attention
+}  // namespace hom

@@ -1,0 +1,35 @@
+// Host interface of the HBM-bound kernels (bandwidth_kernels.cu).
+#pragma once
+
+#include "hom_common.cuh"
+
+namespace hom {
+namespace bw {
+
+// Shapes for the general broadcast path, passed to the kernel by value.
+struct BroadcastShape {
+  int rank = 0;
+  long long out_stride[HOM_MAX_RANK] = {};  // row-major strides of A / Out
+  long long b_size[HOM_MAX_RANK] = {};
+  long long b_stride[HOM_MAX_RANK] = {};
+};
+
+// out = LayerNorm(x [+ res]) [* gamma] [+ beta]; res/gamma/beta may be null; out may alias x.
+bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, const __half *beta,
+                   __half *out, int64_t rows, int64_t hidden, float eps, cudaStream_t stream);
+bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, float eps,
+                   cudaStream_t stream);
+
+// op: 0 add, 1 sub, 2 mul, 3 div.  b_period > 0 means B repeats every b_period elements of
+// the flat output (leading-dimension broadcast or no broadcast); otherwise `sh` is used.
+bool elementwise(int op, bool is_f16, const void *a, const void *b, void *out, int64_t n,
+                 int64_t b_numel, int64_t b_period, const BroadcastShape &sh, cudaStream_t stream);
+
+bool gather_rows(bool is_f16, const int64_t *idx, const void *table, void *out, int64_t rows,
+                 int64_t vocab, int64_t hidden, cudaStream_t stream);
+
+bool cu_seqlen(bool is_i64, const void *mask, int *out, int64_t bs, int64_t seq,
+               cudaStream_t stream);
+
+}  // namespace bw
+}  // namespace hom

@@ -1,0 +1,167 @@
+// Error side channel, per-thread stream, per-device status word, launch counting and
+// per-launch event timing.  The reference has none of this: it aborts the process on any
+// CUDA error (include/NVGPUKernels/Utils.h:45-52) and always uses the null stream.
+#include <atomic>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "hom_common.cuh"
+
+namespace hom {
+
+namespace {
+
+thread_local int tl_error_code = HOM_OK;
+thread_local char tl_error_text[512] = "";
+thread_local cudaStream_t tl_stream = nullptr;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+  std::once_flag once;
+  int *status_host = nullptr;  // pinned, mapped
+  int *status_dev = nullptr;   // device alias of status_host
+  int sm_count = 0;
+};
+DeviceState g_devices[kMaxDevices];
+
+std::atomic<int64_t> g_launch_count{0};
+
+struct TimingRecord {
+  int32_t kind;
+  double flops;
+  double bytes;
+  cudaEvent_t start;
+  cudaEvent_t stop;
+};
+std::mutex g_timing_mutex;
+std::vector<TimingRecord> g_timing_log;
+std::atomic<bool> g_timing_enabled{false};
+
+DeviceState &device_state() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  DeviceState &st = g_devices[dev];
+  std::call_once(st.once, [&st, dev]() {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) == cudaSuccess) st.sm_count = prop.multiProcessorCount;
+    void *host = nullptr;
+    if (cudaHostAlloc(&host, sizeof(int) * 16, cudaHostAllocMapped) == cudaSuccess) {
+      st.status_host = static_cast<int *>(host);
+      for (int i = 0; i < 16; ++i) st.status_host[i] = 0;
+      void *devp = nullptr;
+      if (cudaHostGetDevicePointer(&devp, host, 0) == cudaSuccess)
+        st.status_dev = static_cast<int *>(devp);
+    }
+  });
+  return st;
+}
+
+}  // namespace
+
+void set_error(int code, const char *fmt, ...) {
+  tl_error_code = code;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error_text, sizeof(tl_error_text), fmt, ap);
+  va_end(ap);
+}
+
+bool check_cuda(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return true;
+  set_error(HOM_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return false;
+}
+
+cudaStream_t current_stream() { return tl_stream; }
+
+int *device_status_word() { return device_state().status_dev; }
+
+int sm_count() {
+  int n = device_state().sm_count;
+  return n > 0 ? n : 148;
+}
+
+LaunchScope::LaunchScope(OpKind kind, double flops, double bytes) {
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  if (!g_timing_enabled.load(std::memory_order_relaxed)) return;
+  TimingRecord rec{kind, flops, bytes, nullptr, nullptr};
+  if (cudaEventCreate(&rec.start) != cudaSuccess) return;
+  if (cudaEventCreate(&rec.stop) != cudaSuccess) {
+    cudaEventDestroy(rec.start);
+    return;
+  }
+  cudaEventRecord(rec.start, current_stream());
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  g_timing_log.push_back(rec);
+  slot_ = static_cast<int>(g_timing_log.size()) - 1;
+}
+
+LaunchScope::~LaunchScope() {
+  if (slot_ < 0) return;
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  if (slot_ < static_cast<int>(g_timing_log.size()))
+    cudaEventRecord(g_timing_log[slot_].stop, current_stream());
+}
+
+}  // namespace hom
+
+extern "C" {
+
+int homGetLastError(void) { return hom::tl_error_code; }
+
+const char *homGetLastErrorString(void) { return hom::tl_error_text; }
+
+void homClearLastError(void) {
+  hom::tl_error_code = HOM_OK;
+  hom::tl_error_text[0] = '\0';
+  auto &st = hom::device_state();
+  if (st.status_host) st.status_host[0] = 0;
+}
+
+void homSetStream(void *stream) { hom::tl_stream = static_cast<cudaStream_t>(stream); }
+
+void *homGetStream(void) { return hom::tl_stream; }
+
+int homSynchronize(void) {
+  cudaError_t e = cudaStreamSynchronize(hom::tl_stream);
+  if (e != cudaSuccess) {
+    hom::set_error(HOM_ERR_CUDA, "cudaStreamSynchronize: %s", cudaGetErrorString(e));
+    return hom::tl_error_code;
+  }
+  auto &st = hom::device_state();
+  if (st.status_host && st.status_host[0] != 0) {
+    hom::set_error(HOM_ERR_DEVICE_TIMEOUT, "a device-side wait expired (kernel status %d)",
+                   st.status_host[0]);
+  }
+  return hom::tl_error_code;
+}
+
+int64_t homKernelLaunchCount(void) { return hom::g_launch_count.load(); }
+
+void homOpTimingEnable(int enable) { hom::g_timing_enabled.store(enable != 0); }
+
+int64_t homOpTimingCollect(HomOpTiming *out, int64_t capacity) {
+  cudaDeviceSynchronize();
+  std::lock_guard<std::mutex> lock(hom::g_timing_mutex);
+  const int64_t n = static_cast<int64_t>(hom::g_timing_log.size());
+  for (int64_t i = 0; i < n; ++i) {
+    auto &rec = hom::g_timing_log[i];
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, rec.start, rec.stop) != cudaSuccess) ms = -1.f;
+    if (out && i < capacity) {
+      out[i].kind = rec.kind;
+      out[i].ms = ms;
+      out[i].flops = rec.flops;
+      out[i].bytes = rec.bytes;
+    }
+    cudaEventDestroy(rec.start);
+    cudaEventDestroy(rec.stop);
+  }
+  hom::g_timing_log.clear();
+  return n;
+}
+
+}  // extern "C"

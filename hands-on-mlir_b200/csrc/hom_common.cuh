@@ -1,0 +1,91 @@
+// Internals shared by the runner-utils translation units: memref views, the error
+// side channel, the per-thread launch context and per-launch timing.
+#pragma once
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "hom_nvgpu_runner_utils.h"
+
+namespace hom {
+
+// ------------------------------------------------------------------ memref view
+
+// Host-side view of an unranked memref argument.  The descriptor record is
+// {basePtr, data, offset, sizes[rank], strides[rank]}; `ptr` already includes the offset.
+struct MemRefView {
+  int64_t rank = 0;
+  char *ptr = nullptr;
+  int64_t sizes[HOM_MAX_RANK] = {};
+  int64_t strides[HOM_MAX_RANK] = {};
+  bool valid = false;
+
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int64_t i = 0; i < rank; ++i) n *= sizes[i];
+    return n;
+  }
+  // Row-major contiguous (size-1 dimensions may carry any stride).
+  bool contiguous() const {
+    int64_t expect = 1;
+    for (int64_t i = rank - 1; i >= 0; --i) {
+      if (sizes[i] != 1 && strides[i] != expect) return false;
+      expect *= sizes[i];
+    }
+    return true;
+  }
+};
+
+inline MemRefView view_memref(int64_t rank, void *descriptor, size_t elem_size) {
+  MemRefView v;
+  if (descriptor == nullptr || rank < 0 || rank > HOM_MAX_RANK) return v;
+  auto *words = static_cast<int64_t *>(descriptor);
+  char *data = reinterpret_cast<char *>(static_cast<void **>(descriptor)[1]);
+  const int64_t offset = words[2];
+  v.rank = rank;
+  for (int64_t i = 0; i < rank; ++i) {
+    v.sizes[i] = words[3 + i];
+    v.strides[i] = words[3 + rank + i];
+    if (v.sizes[i] < 0) return v;
+  }
+  v.ptr = data + offset * static_cast<int64_t>(elem_size);
+  v.valid = data != nullptr;
+  return v;
+}
+
+// ---------------------------------------------------------------- error channel
+
+void set_error(int code, const char *fmt, ...);
+bool check_cuda(cudaError_t e, const char *what);  // true when e == cudaSuccess
+
+// ------------------------------------------------------------------ launch context
+
+enum OpKind : int32_t {
+  kOpGemm = 1,
+  kOpLayernorm = 2,
+  kOpAttention = 3,
+  kOpElementwise = 4,
+  kOpGather = 5,
+  kOpCuSeqLen = 6,
+};
+
+cudaStream_t current_stream();
+// Host-mapped status word that device code writes on a bounded-wait expiry (device pointer).
+int *device_status_word();
+int sm_count();
+
+// RAII bracket around one kernel launch: counts it and, when timing is enabled,
+// records events on the current stream.
+class LaunchScope {
+ public:
+  LaunchScope(OpKind kind, double flops, double bytes);
+  ~LaunchScope();
+
+ private:
+  int slot_ = -1;
+};
+
+}  // namespace hom

@@ -1,0 +1,213 @@
+/* C ABI of libhands_on_mlir_nvgpu_runner_utils.so, the runtime kernel layer that a
+ * BERT model lowered by Hands-on-MLIR calls into.
+ *
+ * Part 1 declares, with identical names and argument lists, every entry point of
+ * the reference's include/ExecutionEngine/HandsOnNVGPURunnerUtils.h:70-164 (the
+ * symbol names the lowering emits are listed in
+ * include/Conversions/Function/FunctionUtils.h:12-49).  A model .so produced by
+ * the reference's compiler links against this library unchanged.
+ *
+ * Part 2 declares additions (prefix `hom`) that have no counterpart in the
+ * reference: an error side channel (the reference aborts the process instead),
+ * stream selection (the reference always uses the null stream), the
+ * residual+affine LayerNorm of the op-level benchmark configuration, and
+ * measurement hooks.
+ *
+ * Conventions shared by all compute entry points:
+ *  - tensors are `(int64_t rank, void *descriptor)` pairs, see hom_memref.h;
+ *    data must be row-major contiguous; `offset` is honoured.
+ *  - work is enqueued on the library's current stream (null stream unless
+ *    homSetStream() was called) of the current CUDA device and is not awaited.
+ *  - nothing is returned; a rejected call launches nothing and records an error
+ *    that homGetLastError() reports.  The process is never aborted.
+ */
+#ifndef HOM_NVGPU_RUNNER_UTILS_H
+#define HOM_NVGPU_RUNNER_UTILS_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#include "hom_memref.h"
+
+#if defined(__GNUC__)
+#define HOM_EXPORT __attribute__((visibility("default")))
+#else
+#define HOM_EXPORT
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===================================================================== Part 1 */
+
+/* D = epilogue(alpha * A.B + beta * C); A [Bs,M,K], B [1,K,N], C/D [Bs,M,N], fp16 in and
+ * out, fp32 accumulate and epilogue.  `activation` 1 = erf GELU, 0 = identity.  D may alias C.
+ * C may also be [1,1,N] (bias broadcast over rows, as the reference's CPU matmulAddF32 does,
+ * lib/ExecutionEngine/HandsOnRunnerUtils.cpp:258-266).  `gemmNum` > 0 selects a row of the
+ * sm_100a tile table (0 or an unknown number = automatic); `splitKFactor` is a hint.
+ * Replaces lib/ExecutionEngine/HandsOnNVGPURunnerUtils.cu:104-116 and
+ * include/NVGPUKernels/GemmRunner.h:244-310. */
+HOM_EXPORT void cutlassGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *dstB,
+                               bool transb, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                               int64_t activation, float alpha, float beta, int32_t gemmNum,
+                               int32_t splitKFactor);
+
+/* Empty stub in the reference (HandsOnNVGPURunnerUtils.cu:80-102); records "unsupported". */
+HOM_EXPORT void cutlassGemmF32(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *dstB,
+                               bool transb, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                               int64_t activation, float alpha, float beta);
+
+/* D = act(A.B^T) (+ D when beta == 1 and C aliases D); A [Bs,M,K], B [1,N,K] with
+ * transb == true, transa == false, alpha == 1, beta in {0,1}.
+ * Replaces HandsOnNVGPURunnerUtils.cu:172-183 and GemmRunner.h:322-426. */
+HOM_EXPORT void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *dstB,
+                            bool transb, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                            int64_t activation, float alpha, float beta, int32_t unused0,
+                            int32_t unused1);
+
+/* GEMM whose epilogue also emits per-row partial statistics, and the GEMM that consumes
+ * them (HandsOnNVGPURunnerUtils.cu:118-170, :191-222).  Not emitted by the compiler for
+ * BERT; exported for link parity. */
+HOM_EXPORT void cutlassGemmWithVarMeanF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
+                                          int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                                          int64_t rankVar, void *dstVar, int64_t rankMean,
+                                          void *dstMean, float alpha, float beta,
+                                          int64_t activation, float eps);
+HOM_EXPORT void cutlassLayernormGemmF32(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
+                                        int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                                        int64_t rankVar, void *dstVar, int64_t rankMean,
+                                        void *dstMean, float alpha, float beta,
+                                        int64_t activation);
+HOM_EXPORT void cutlassLayernormGemmF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
+                                        int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                                        int64_t rankVar, void *dstVar, int64_t rankMean,
+                                        void *dstMean, float alpha, float beta,
+                                        int64_t activation);
+
+/* In-place x <- (x - mean) * rsqrt(var + eps) over the last dimension, biased variance,
+ * fp32 statistics, no affine; rank 2 or 3.
+ * Replaces HandsOnNVGPURunnerUtils.cu:300-310 and include/NVGPUKernels/Layernorm.h:584-694. */
+HOM_EXPORT void nvteLayernormF32(int64_t rankA, void *dstA, float eps);
+HOM_EXPORT void nvteLayernormF16(int64_t rankA, void *dstA, float eps);
+
+/* O = softmax(scale * Q.K^T + padding mask).V per (batch, head), bidirectional.
+ * A = packed QKV [bs, seq, 3*heads*d] with innermost order [3][heads][d];
+ * Seqlen = int32 [bs+1] prefix sums of valid lengths; Out [bs, seq, heads*d].
+ * Rows at padded query positions are written as zeros.
+ * Replaces HandsOnNVGPURunnerUtils.cu:312-328 and
+ * include/NVGPUKernels/BertAttentionRunner.h:19-137. */
+HOM_EXPORT void nvteBertAttentionF32(int64_t rankA, void *dstA, int64_t rankSeqlen,
+                                     void *dstSeqlen, int64_t rankOut, void *dstOut, float scale,
+                                     int64_t headNum);
+HOM_EXPORT void nvteBertAttentionF16(int64_t rankA, void *dstA, int64_t rankSeqlen,
+                                     void *dstSeqlen, int64_t rankOut, void *dstOut, float scale,
+                                     int64_t headNum);
+
+/* Device allocation.  The descriptor is malloc()ed (callers free() it); the buffer is
+ * released by dealloc*.  allocConstant* reads "<dir>/<idx>.txt" (first line: three
+ * dimensions; then the values as text) and uploads it, converting to fp16 with
+ * round-to-nearest-even for the F16 variant.
+ * Replaces HandsOnNVGPURunnerUtils.cu:224-355 and allocHelper,
+ * include/ExecutionEngine/HandsOnRunnerUtils.h:46-73. */
+HOM_EXPORT HomUnrankedMemRef allocConstantNVGPUF32(int32_t idx);
+HOM_EXPORT HomUnrankedMemRef allocConstantNVGPUF16(int32_t idx);
+HOM_EXPORT HomUnrankedMemRef alloc3DMemRefNVGPUF32(int32_t a, int32_t b, int32_t c);
+HOM_EXPORT HomUnrankedMemRef alloc3DMemRefNVGPUF16(int32_t a, int32_t b, int32_t c);
+HOM_EXPORT HomUnrankedMemRef alloc1DMemRefNVGPUI32(int32_t n);
+HOM_EXPORT void deallocNVGPUF32(int64_t rank, void *dst);
+HOM_EXPORT void deallocNVGPUF16(int64_t rank, void *dst);
+HOM_EXPORT void deallocNVGPUI32(int64_t rank, void *dst);
+
+/* Out = A op B; same rank; B may have size-1 (broadcast) dimensions; arithmetic in the
+ * element type.  Replaces HandsOnNVGPURunnerUtils.cu:357-365 and
+ * include/NVGPUKernels/ElementwiseRunner.h:120-153. */
+HOM_EXPORT void thrustElementwiseAddF32(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseSubF32(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseMulF32(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseDivF32(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseAddF16(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseSubF16(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseMulF16(int64_t, void *, int64_t, void *, int64_t, void *);
+HOM_EXPORT void thrustElementwiseDivF16(int64_t, void *, int64_t, void *, int64_t, void *);
+
+/* out[b,s,:] = table[0, indices[b,s], :]; indices int64 [bs,seq]; table [1,V,H].
+ * Replaces HandsOnNVGPURunnerUtils.cu:367-368 and include/NVGPUKernels/GatherRunner.h:46-77. */
+HOM_EXPORT void thrustGatherF32(int64_t rankIndices, void *desIndices, int64_t rankValue,
+                                void *desValue, int64_t rankOut, void *desOut);
+HOM_EXPORT void thrustGatherF16(int64_t rankIndices, void *desIndices, int64_t rankValue,
+                                void *desValue, int64_t rankOut, void *desOut);
+
+/* out[0] = 0; out[b+1] = sum over rows <= b of sum_j mask[row][j]; mask [bs,seq] int32/int64,
+ * out int32 [bs+1].  Replaces HandsOnNVGPURunnerUtils.cu:370-371 and
+ * include/NVGPUKernels/CuSeqLen.h:48-74. */
+HOM_EXPORT void thrustCuSeqLenI32(int64_t rankInput, void *desInput, int64_t rankOut, void *desOut);
+HOM_EXPORT void thrustCuSeqLenI64(int64_t rankInput, void *desInput, int64_t rankOut, void *desOut);
+
+/* Prints "Print inside: <sizes>" to stderr (HandsOnNVGPURunnerUtils.h:58-68). */
+HOM_EXPORT void printMemrefSizeF32(int64_t rank, void *descriptor);
+HOM_EXPORT void printMemrefSizeF16(int64_t rank, void *descriptor);
+HOM_EXPORT void printMemrefSizeI64(int64_t rank, void *descriptor);
+HOM_EXPORT void printMemrefSizeI32(int64_t rank, void *descriptor);
+
+/* ===================================================================== Part 2 */
+
+/* Error side channel (per host thread).  Codes: 0 ok, 1 invalid argument, 2 unsupported,
+ * 3 CUDA runtime error, 4 device-side wait expired, 5 I/O error. */
+enum {
+  HOM_OK = 0,
+  HOM_ERR_INVALID = 1,
+  HOM_ERR_UNSUPPORTED = 2,
+  HOM_ERR_CUDA = 3,
+  HOM_ERR_DEVICE_TIMEOUT = 4,
+  HOM_ERR_IO = 5
+};
+HOM_EXPORT int homGetLastError(void);
+HOM_EXPORT const char *homGetLastErrorString(void);
+HOM_EXPORT void homClearLastError(void);
+
+/* Stream used by this host thread's subsequent calls (a cudaStream_t; NULL = null stream). */
+HOM_EXPORT void homSetStream(void *stream);
+HOM_EXPORT void *homGetStream(void);
+/* Waits for the stream, then folds the device status word into the error channel.
+ * Returns the error code. */
+HOM_EXPORT int homSynchronize(void);
+
+/* Directory that allocConstantNVGPU* reads "<idx>.txt" from (default: $HOM_CONSTANT_DIR,
+ * else the current directory). */
+HOM_EXPORT void homSetConstantDir(const char *dir);
+
+/* Out = LayerNorm(X + R) * gamma + beta over the last dimension; X, R, Out [rows.., H]
+ * fp16 (R, gamma, beta may be rank-0 descriptors = absent), fp32 sum and statistics,
+ * one fp16 rounding at the store.  Out may alias X. */
+HOM_EXPORT void homResidualLayernormF16(int64_t rankX, void *dstX, int64_t rankR, void *dstR,
+                                        int64_t rankGamma, void *dstGamma, int64_t rankBeta,
+                                        void *dstBeta, int64_t rankOut, void *dstOut, float eps);
+
+/* Number of kernels this library has launched since load (all threads). */
+HOM_EXPORT int64_t homKernelLaunchCount(void);
+
+/* Per-launch timing: while enabled every entry point brackets its kernel with events on
+ * the current stream.  homOpTimingCollect() synchronises, writes up to `capacity` records
+ * (kind: 1 gemm, 2 layernorm, 3 attention, 4 elementwise, 5 gather, 6 cu_seqlen; ms; and
+ * the algorithmic flop and byte counts of that launch), clears the log and returns the
+ * number of records that were available. */
+typedef struct HomOpTiming {
+  int32_t kind;
+  float ms;
+  double flops;
+  double bytes;
+} HomOpTiming;
+HOM_EXPORT void homOpTimingEnable(int enable);
+HOM_EXPORT int64_t homOpTimingCollect(HomOpTiming *out, int64_t capacity);
+
+/* The tile the GEMM family would run for (M, N, K, activation): BN (tile is 128 x BN x 64),
+ * pipeline stages and split-K.  Returns the tile-table row number (usable as gemmNum). */
+HOM_EXPORT int32_t homGemmQueryTile(int64_t m, int64_t n, int64_t k, int64_t activation,
+                                    int32_t *bn, int32_t *stages, int32_t *splitK);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HOM_NVGPU_RUNNER_UTILS_H */

@@ -1,0 +1,339 @@
+"""GPU parity tests: every runner-utils entry point, called through the C ABI with device
+tensors, against the CPU oracle on the same seeded inputs.
+
+Tolerance: fp16 rtol 1e-3 / atol 1e-3 for the floating-point kernels (GEMM, LayerNorm,
+attention); bit-exact for elementwise, gather, cu_seqlens and the constant loader.
+"""
+import numpy as np
+import pytest
+
+from util import assert_bits_equal, assert_close_f16, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+# ------------------------------------------------------------------------ GEMM
+
+def _run_gemm(hom, dev, A, B, C, *, nk=False, act=0, alpha=1.0, beta=0.0, tile=0, alias=False):
+    import torch
+    tA, tB = to_dev(A, dev), to_dev(B, dev)
+    n = B.shape[-2] if nk else B.shape[-1]
+    if alias:
+        tD = to_dev(C, dev)
+        tC = tD
+    else:
+        tD = torch.full(A.shape[:-1] + (n,), float("nan"), dtype=torch.float16, device=dev)
+        tC = to_dev(C, dev) if C is not None else tD
+    if nk:
+        hom.nvteGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta)
+    else:
+        hom.cutlassGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta, gemmNum=tile)
+    hom.synchronize()
+    return tD.cpu().numpy()
+
+
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("shape", [(1, 128, 64, 64), (2, 128, 256, 128), (1, 200, 136, 72),
+                                   (3, 100, 520, 200), (1, 384, 768, 1024)])
+def test_gemm_plain_all_tiles(hom, cuda, oracle, shape, tile):
+    bs, m, n, k = shape
+    rng = _rng(1)
+    A = rng.uniform(-1, 1, (bs, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.05, (1, k, n)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, None, tile=tile)
+    assert_close_f16(got, oracle.gemm_f16(A, B), f"gemm {shape} tile {tile}")
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4])
+def test_gemm_bias_gelu_config1(hom, cuda, oracle, seed):
+    """A[512x768] U(-1,1), bias[3072] U(-1,1), B[768x3072] N(0,0.02): fused bias + erf GELU."""
+    rng = _rng(seed)
+    A = rng.uniform(-1, 1, (4, 128, 768)).astype(np.float32).astype(np.float16)
+    bias = rng.uniform(-1, 1, (1, 1, 3072)).astype(np.float32).astype(np.float16)
+    B = rng.normal(0, 0.02, (1, 768, 3072)).astype(np.float32).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, bias, act=1, beta=1.0)
+    assert_close_f16(got, oracle.gemm_f16(A, B, bias, beta=1.0, act=1), "config 1")
+
+
+@pytest.mark.parametrize("tile", [0, 2, 3, 4])
+def test_gemm_residual_aliases_output(hom, cuda, oracle, tile):
+    rng = _rng(7)
+    A = rng.normal(0, 1, (2, 128, 256)).astype(np.float16)
+    B = rng.normal(0, 0.05, (1, 256, 768)).astype(np.float16)
+    C = rng.normal(0, 1, (2, 128, 768)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, C, beta=1.0, alias=True, tile=tile)
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, beta=1.0), "residual C==D")
+
+
+def test_gemm_alpha_beta_gelu(hom, cuda, oracle):
+    rng = _rng(8)
+    A = rng.normal(0, 1, (1, 256, 192)).astype(np.float16)
+    B = rng.normal(0, 0.1, (1, 192, 320)).astype(np.float16)
+    C = rng.normal(0, 1, (1, 256, 320)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, C, alpha=0.5, beta=-1.5, act=1)
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, alpha=0.5, beta=-1.5, act=1), "alpha/beta")
+
+
+@pytest.mark.parametrize("shape", [(2, 128, 256, 128), (1, 300, 1024, 264), (4, 128, 768, 3072)])
+@pytest.mark.parametrize("act,beta", [(0, 0.0), (1, 0.0), (0, 1.0)])
+def test_nvte_gemm_transb(hom, cuda, oracle, shape, act, beta):
+    bs, m, n, k = shape
+    rng = _rng(11)
+    A = rng.uniform(-1, 1, (bs, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.03, (1, n, k)).astype(np.float16)
+    C = rng.normal(0, 1, (bs, m, n)).astype(np.float16) if beta else None
+    got = _run_gemm(hom, cuda, A, B, C, nk=True, act=act, beta=beta, alias=bool(beta))
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, b_is_nk=True, act=act, beta=beta),
+                     f"nvte {shape} act {act} beta {beta}")
+
+
+def test_gemm_constant_inputs_like_reference_harness(hom, cuda):
+    """A = 0.1, B = 0.2, 512x768x768: every output is K * 0.02 within 1e-1
+    (the check of examples/torch/linear/cuda/b.cu:17-66)."""
+    A = np.full((1, 512, 768), 0.1, np.float16)
+    B = np.full((1, 768, 768), 0.2, np.float16)
+    got = _run_gemm(hom, cuda, A, B, None).astype(np.float32)
+    assert np.abs(got - 768 * 0.02).max() <= 1e-1
+
+
+@pytest.mark.parametrize("m,n,k,act,res", [(4096, 2304, 768, 0, False), (4096, 768, 768, 0, True),
+                                           (4096, 3072, 768, 1, False), (4096, 768, 3072, 0, True)])
+def test_gemm_bert_base_shapes_sampled_rows(hom, cuda, oracle, m, n, k, act, res):
+    """BERT-base b32 x s128 GEMMs at full size; the oracle checks 3 rows of every 128-row block."""
+    rng = _rng(21)
+    A = rng.normal(0, 1, (32, 128, k)).astype(np.float16)
+    B = rng.normal(0, 0.02, (1, k, n)).astype(np.float16)
+    C = rng.normal(0, 1, (32, 128, n)).astype(np.float16) if res else None
+    got = _run_gemm(hom, cuda, A, B, C, act=act, beta=1.0 if res else 0.0, alias=res)
+    rows = np.concatenate([np.arange(0, m, 128), np.arange(77, m, 128), np.arange(127, m, 128)])
+    A2, got2 = A.reshape(m, k)[rows], got.reshape(m, n)[rows]
+    C2 = C.reshape(m, n)[rows] if res else None
+    want = oracle.gemm_f16(A2, B, C2, act=act, beta=1.0 if res else 0.0)
+    assert_close_f16(got2, want, f"bert-base gemm {m}x{n}x{k}")
+    assert np.isfinite(got.astype(np.float32)).all()
+
+
+def test_gemm_rejects_bad_arguments(hom, cuda, pkg):
+    import torch
+    A = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
+    B = torch.zeros((1, 72, 64), dtype=torch.float16, device=cuda)  # K mismatch
+    D = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
+    before = hom.launch_count()
+    with pytest.raises(pkg.HomError) as e:
+        hom.cutlassGemmF16(A, B, D, D)
+    assert e.value.code == 1
+    B2 = torch.zeros((1, 64, 60), dtype=torch.float16, device=cuda)  # N % 8 != 0
+    D2 = torch.zeros((1, 128, 60), dtype=torch.float16, device=cuda)
+    with pytest.raises(pkg.HomError) as e:
+        hom.cutlassGemmF16(A, B2, D2, D2)
+    assert e.value.code == 2
+    with pytest.raises(pkg.HomError):
+        hom.nvteGemmF16(A, B, D, D, transb=False)
+    assert hom.launch_count() == before
+
+
+# ------------------------------------------------------------------- LayerNorm
+
+def test_layernorm_inplace_reference_literal(hom, cuda, oracle):
+    """The 2x10 fp32 input of examples/torch/layernorm/cuda/layernorm.cu:24-26."""
+    from golden.reference_literals import LAYERNORM_2x10
+    x = LAYERNORM_2x10.copy()
+    t = to_dev(x, cuda)
+    hom.nvteLayernormF32(t, 1e-5)
+    hom.synchronize()
+    np.testing.assert_allclose(t.cpu().numpy(), oracle.layernorm_f32(x, 1e-5), rtol=1e-5, atol=1e-5)
+    xh = x.astype(np.float16)
+    th = to_dev(xh, cuda)
+    hom.nvteLayernormF16(th, 1e-5)
+    hom.synchronize()
+    assert_close_f16(th.cpu().numpy(), oracle.layernorm_f16(xh, 1e-5), "ln 2x10 f16")
+
+
+@pytest.mark.parametrize("shape", [(32, 128, 768), (4, 512, 1024), (7, 33, 264), (5, 3, 4096),
+                                   (16, 50)])
+def test_layernorm_inplace(hom, cuda, oracle, shape):
+    x = _rng(3).normal(0.3, 1.7, shape).astype(np.float16)
+    t = to_dev(x, cuda)
+    hom.nvteLayernormF16(t, 1e-12)
+    hom.synchronize()
+    assert_close_f16(t.cpu().numpy(), oracle.layernorm_f16(x, 1e-12), f"ln {shape}")
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4])
+def test_residual_layernorm_config2(hom, cuda, oracle, seed):
+    """X, R [4096x768] N(0,1); gamma = 1 + N(0,0.1), beta = N(0,0.1); eps 1e-12."""
+    import torch
+    rng = _rng(seed)
+    x = rng.normal(0, 1, (4096, 768)).astype(np.float32).astype(np.float16)
+    r = rng.normal(0, 1, (4096, 768)).astype(np.float32).astype(np.float16)
+    g = (1 + rng.normal(0, 0.1, 768)).astype(np.float32).astype(np.float16)
+    b = rng.normal(0, 0.1, 768).astype(np.float32).astype(np.float16)
+    out = torch.empty((4096, 768), dtype=torch.float16, device=cuda)
+    hom.homResidualLayernormF16(to_dev(x, cuda), to_dev(r, cuda), to_dev(g, cuda), to_dev(b, cuda),
+                                out, 1e-12)
+    hom.synchronize()
+    assert_close_f16(out.cpu().numpy(), oracle.layernorm_f16(x, 1e-12, r, g, b), "config 2")
+
+
+def test_layernorm_f32(hom, cuda, oracle):
+    x = _rng(5).normal(0, 2, (3, 17, 100)).astype(np.float32)
+    t = to_dev(x, cuda)
+    hom.nvteLayernormF32(t, 1e-6)
+    hom.synchronize()
+    np.testing.assert_allclose(t.cpu().numpy(), oracle.layernorm_f32(x, 1e-6), rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------- attention
+
+def _attention_case(hom, dev, oracle, bs, seq, heads, lens, seed):
+    import torch
+    rng = _rng(seed)
+    qkv = rng.normal(0, 1, (bs, seq, 3 * heads * 64)).astype(np.float32).astype(np.float16)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    out = torch.full((bs, seq, heads * 64), float("nan"), dtype=torch.float16, device=dev)
+    hom.nvteBertAttentionF16(to_dev(qkv, dev), to_dev(cu, dev), out, 0.125, heads)
+    hom.synchronize()
+    want = oracle.attention_f16(qkv, cu, heads, 0.125)
+    assert_close_f16(out.cpu().numpy(), want, f"attention bs{bs} seq{seq} heads{heads}")
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_attention_config3(hom, cuda, oracle, seed):
+    """QKV [32,128,3,12,64] N(0,1), valid lengths U{64..128}, scale 1/8."""
+    lens = _rng(100 + seed).integers(64, 129, 32)
+    _attention_case(hom, cuda, oracle, 32, 128, 12, lens, seed)
+
+
+def test_attention_edge_lengths(hom, cuda, oracle):
+    _attention_case(hom, cuda, oracle, 6, 128, 2, np.array([1, 128, 0, 2, 127, 64]), 5)
+
+
+def test_attention_seq512_multi_tile(hom, cuda, oracle):
+    _attention_case(hom, cuda, oracle, 4, 512, 3, np.array([512, 256, 257, 130]), 6)
+
+
+def test_attention_seq_not_multiple_of_tile(hom, cuda, oracle):
+    _attention_case(hom, cuda, oracle, 3, 192, 2, np.array([192, 100, 129]), 7)
+
+
+def test_attention_rejects_head_dim(hom, cuda, pkg):
+    import torch
+    qkv = torch.zeros((1, 128, 3 * 2 * 32), dtype=torch.float16, device=cuda)
+    cu = torch.zeros(2, dtype=torch.int32, device=cuda)
+    out = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(pkg.HomError) as e:
+        hom.nvteBertAttentionF16(qkv, cu, out, 0.125, 2)
+    assert e.value.code == 2
+
+
+# ------------------------------------------------ elementwise / gather / cu_seqlen
+
+def test_elementwise_reference_literal(hom, cuda, oracle):
+    """3x3x3 + 3x1x3 broadcast add with the fp32 inputs of examples/torch/elementwise/add.cu:21-26."""
+    import torch
+    from golden.reference_literals import ADD_A_3x3x3, ADD_B_3x1x3
+    a, b = ADD_A_3x3x3, ADD_B_3x1x3
+    out = torch.empty((3, 3, 3), dtype=torch.float32, device=cuda)
+    hom.elementwise("Add", "F32", to_dev(a, cuda), to_dev(b, cuda), out)
+    hom.synchronize()
+    assert_bits_equal(out.cpu().numpy(), oracle.elementwise("Add", a, b), "add literal")
+    assert_bits_equal(out.cpu().numpy(), a + b, "add literal vs numpy")
+    ah, bh = a.astype(np.float16), b.astype(np.float16)
+    outh = torch.empty((3, 3, 3), dtype=torch.float16, device=cuda)
+    hom.thrustElementwiseAddF16(to_dev(ah, cuda), to_dev(bh, cuda), outh)
+    hom.synchronize()
+    assert_bits_equal(outh.cpu().numpy(), ah + bh, "add literal f16 vs numpy")
+
+
+@pytest.mark.parametrize("op", ["Add", "Sub", "Mul", "Div"])
+@pytest.mark.parametrize("dtype", ["F16", "F32"])
+@pytest.mark.parametrize("shapes", [((32, 128, 768), (32, 128, 768)), ((32, 128, 768), (1, 128, 768)),
+                                    ((4, 5, 6), (4, 1, 6)), ((4, 5, 6), (1, 1, 1)),
+                                    ((3, 7, 10), (3, 7, 1)), ((6, 9), (1, 9))])
+def test_elementwise_bit_exact(hom, cuda, oracle, op, dtype, shapes):
+    import torch
+    np_t = np.float16 if dtype == "F16" else np.float32
+    rng = _rng(9)
+    a = rng.normal(0, 1, shapes[0]).astype(np_t)
+    b = (rng.normal(0, 1, shapes[1]) + 3.0).astype(np_t)
+    out = torch.empty(shapes[0], dtype=torch.float16 if dtype == "F16" else torch.float32, device=cuda)
+    hom.elementwise(op, dtype, to_dev(a, cuda), to_dev(b, cuda), out)
+    hom.synchronize()
+    assert_bits_equal(out.cpu().numpy(), oracle.elementwise(op, a, b), f"{op}{dtype} {shapes}")
+
+
+@pytest.mark.parametrize("dtype,hidden", [("F16", 768), ("F16", 1024), ("F16", 10), ("F32", 36)])
+def test_gather(hom, cuda, oracle, dtype, hidden):
+    import torch
+    np_t = np.float16 if dtype == "F16" else np.float32
+    rng = _rng(4)
+    table = rng.normal(0, 1, (1, 1000, hidden)).astype(np_t)
+    idx = rng.integers(0, 1000, (8, 128)).astype(np.int64)
+    out = torch.empty((8, 128, hidden), dtype=torch.float16 if dtype == "F16" else torch.float32,
+                      device=cuda)
+    hom.gather(dtype, to_dev(idx, cuda), to_dev(table, cuda), out)
+    hom.synchronize()
+    assert_bits_equal(out.cpu().numpy(), oracle.gather(idx, table), f"gather {dtype} {hidden}")
+
+
+def test_cu_seqlen_reference_table(hom, cuda, oracle):
+    """Valid lengths {64,12,31,32,33,34,35,36} repeated for bs 16, seq 64
+    (examples/torch/bert_attention/cuSeqLen.cu:26-33)."""
+    import torch
+    lens = np.array([64, 12, 31, 32, 33, 34, 35, 36] * 2)
+    mask = (np.arange(64)[None, :] < lens[:, None]).astype(np.int64)
+    out = torch.full((17,), -1, dtype=torch.int32, device=cuda)
+    hom.thrustCuSeqLenI64(to_dev(mask, cuda), out)
+    hom.synchronize()
+    want = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    np.testing.assert_array_equal(oracle.cu_seqlen(mask), want)
+
+
+@pytest.mark.parametrize("dtype,bs,seq", [("I64", 256, 512), ("I32", 3000, 17), ("I64", 1, 1),
+                                          ("I32", 32, 128)])
+def test_cu_seqlen_sizes(hom, cuda, oracle, dtype, bs, seq):
+    import torch
+    rng = _rng(12)
+    lens = rng.integers(0, seq + 1, bs)
+    mask = (np.arange(seq)[None, :] < lens[:, None]).astype(np.int64 if dtype == "I64" else np.int32)
+    out = torch.full((bs + 1,), -1, dtype=torch.int32, device=cuda)
+    hom.cu_seqlen(dtype, to_dev(mask, cuda), out)
+    hom.synchronize()
+    np.testing.assert_array_equal(out.cpu().numpy(), oracle.cu_seqlen(mask))
+
+
+# ------------------------------------------------------------ allocation / constants
+
+def test_alloc_and_constant_loader(hom, cuda, oracle, tmp_path):
+    import torch
+    vals = _rng(2).normal(0, 0.02, (1, 24, 40)).astype(np.float32)
+    with open(tmp_path / "7.txt", "w") as f:
+        f.write("1 24 40\n")
+        f.write(" ".join(repr(float(v)) for v in vals.ravel()))
+        f.write("\n")
+    hom.lib.homSetConstantDir(str(tmp_path).encode())
+    m = hom.allocConstantNVGPUF16(7)
+    assert m.shape == [1, 24, 40] and m.strides == [960, 40, 1]
+    # read the library-owned buffer back with an identity gather (rows 0..23 of the table)
+    buf = torch.empty((1, 24, 40), dtype=torch.float16, device=cuda)
+    rows = torch.arange(24, dtype=torch.int64, device=cuda).reshape(1, 24)
+    hom.gather("F16", rows, m, buf)
+    hom.synchronize()
+    got = buf.cpu().numpy()
+    want = oracle.f32_to_f16(oracle.parse_constant_text(tmp_path / "7.txt"))
+    assert_bits_equal(got, want, "constant F16")
+    hom.dealloc("F16", m)
+
+    d3 = hom.alloc3DMemRefNVGPUF16(2, 3, 8)
+    assert d3.shape == [2, 3, 8] and d3.strides == [24, 8, 1] and d3.data_ptr != 0
+    hom.dealloc("F16", d3)
+    d1 = hom.alloc1DMemRefNVGPUI32(33)
+    assert d1.shape == [33] and d1.strides == [1]
+    hom.dealloc("I32", d1)
+    with pytest.raises(Exception):
+        hom.allocConstantNVGPUF16(12345)  # missing file -> I/O error, no abort

@@ -1,0 +1,36 @@
+"""Helpers shared by the parity tests."""
+import numpy as np
+
+RTOL = 1e-3  # fp16 parity tolerance stated for this path: rtol 1e-3 / atol 1e-3
+ATOL = 1e-3
+
+
+def to_dev(x, dev):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+
+def assert_close_f16(got, want, what="", rtol=RTOL, atol=ATOL):
+    got = np.asarray(got).astype(np.float64)
+    want = np.asarray(want).astype(np.float64)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    err = np.abs(got - want)
+    tol = atol + rtol * np.abs(want)
+    bad = ~(err <= tol)
+    if bad.any():
+        idx = np.unravel_index(np.argmax(np.where(bad, err, 0)), err.shape)
+        raise AssertionError(
+            f"{what}: {bad.sum()} of {bad.size} elements outside rtol={rtol} atol={atol}; "
+            f"worst at {idx}: got {got[idx]!r} want {want[idx]!r} (max abs err {err.max():.3e})")
+
+
+def assert_bits_equal(got, want, what=""):
+    got, want = np.asarray(got), np.asarray(want)
+    assert got.shape == want.shape and got.dtype == want.dtype, (got.shape, want.shape)
+    g = got.view(np.uint16 if got.dtype == np.float16 else np.uint32 if got.dtype == np.float32 else got.dtype)
+    w = want.view(g.dtype)
+    if not np.array_equal(g, w):
+        bad = np.argwhere(g != w)
+        i = tuple(bad[0])
+        raise AssertionError(f"{what}: {len(bad)} elements differ bitwise; first at {i}: "
+                             f"got {got[i]!r} want {want[i]!r}")
