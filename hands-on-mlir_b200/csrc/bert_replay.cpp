@@ -1,0 +1,300 @@
+// BERT call-sequence replay: the host program a model lowered by Hands-on-MLIR amounts to,
+// written by hand because the MLIR toolchain is not available.  It touches tensors only
+// through the runner-utils C ABI (hom_nvgpu_runner_utils.h); the CUDA runtime is used for
+// stream capture / graph replay and for the host<->device copies of the end-to-end step.
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "hom_bert_replay.h"
+
+namespace {
+
+struct Tensor {
+  int64_t rank = 0;
+  void *desc = nullptr;  // {basePtr, data, offset, sizes[rank], strides[rank]}
+  bool owned_buffer = false;
+  bool owned_desc = false;
+
+  void *data() const { return desc ? static_cast<void **>(desc)[1] : nullptr; }
+};
+
+Tensor from_alloc(HomUnrankedMemRef m) {
+  Tensor t;
+  t.rank = m.rank;
+  t.desc = m.descriptor;
+  t.owned_buffer = t.owned_desc = true;
+  return t;
+}
+
+// A descriptor over caller-owned or program-owned device memory.
+Tensor make_view(void *data, std::initializer_list<int64_t> sizes) {
+  Tensor t;
+  t.rank = static_cast<int64_t>(sizes.size());
+  auto *w = static_cast<int64_t *>(std::malloc(sizeof(int64_t) * (3 + 2 * t.rank)));
+  reinterpret_cast<void **>(w)[0] = data;
+  reinterpret_cast<void **>(w)[1] = data;
+  w[2] = 0;
+  int64_t i = 0;
+  for (int64_t s : sizes) w[3 + i++] = s;
+  int64_t stride = 1;
+  for (int64_t d = t.rank - 1; d >= 0; --d) {
+    w[3 + t.rank + d] = stride;
+    stride *= w[3 + d];
+  }
+  t.desc = w;
+  t.owned_desc = true;
+  return t;
+}
+
+struct Program {
+  HomBertConfig cfg{};
+  std::vector<Tensor> weights;
+  Tensor x, type_rows, qkv, ctx, ffn, cu;  // activations (hoisted allocations)
+  Tensor ids_dev, mask_dev, types_dev;     // staging for the host entry point
+  cudaStream_t own_stream = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  void *graph_ids = nullptr, *graph_mask = nullptr, *graph_types = nullptr;
+  bool warmed_up = false;
+};
+
+void release(Tensor &t, bool f16) {
+  if (t.desc) {
+    if (t.owned_buffer) {
+      if (f16) deallocNVGPUF16(t.rank, t.desc);
+      else deallocNVGPUI32(t.rank, t.desc);
+    }
+    if (t.owned_desc) std::free(t.desc);
+  }
+  t = Tensor{};
+}
+
+int status() { return homGetLastError(); }
+
+// The straight-line call sequence of `_hom_forward`.
+int issue_forward(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void *mask,
+                  int64_t rankTypes, void *types) {
+  const HomBertConfig &c = p.cfg;
+  const float scale = 1.0f / std::sqrt(static_cast<float>(c.hidden / c.heads));
+  auto gemm = [&](Tensor &a, Tensor &w, Tensor &cmat, Tensor &d, int64_t act, float beta) {
+    if (c.weights_nk)
+      nvteGemmF16(a.rank, a.desc, false, w.rank, w.desc, true, cmat.rank, cmat.desc, d.rank, d.desc,
+                  act, 1.0f, beta, 0, 0);
+    else
+      cutlassGemmF16(a.rank, a.desc, false, w.rank, w.desc, false, cmat.rank, cmat.desc, d.rank,
+                     d.desc, act, 1.0f, beta, 0, 1);
+  };
+  thrustCuSeqLenI64(rankMask, mask, p.cu.rank, p.cu.desc);
+  thrustGatherF16(rankIds, ids, p.weights[0].rank, p.weights[0].desc, p.x.rank, p.x.desc);
+  thrustGatherF16(rankTypes, types, p.weights[2].rank, p.weights[2].desc, p.type_rows.rank,
+                  p.type_rows.desc);
+  thrustElementwiseAddF16(p.x.rank, p.x.desc, p.type_rows.rank, p.type_rows.desc, p.x.rank, p.x.desc);
+  thrustElementwiseAddF16(p.x.rank, p.x.desc, p.weights[1].rank, p.weights[1].desc, p.x.rank,
+                          p.x.desc);
+  nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+  for (int l = 0; l < c.layers; ++l) {
+    Tensor &wqkv = p.weights[3 + 4 * l], &wo = p.weights[4 + 4 * l];
+    Tensor &w1 = p.weights[5 + 4 * l], &w2 = p.weights[6 + 4 * l];
+    gemm(p.x, wqkv, p.qkv, p.qkv, 0, 0.0f);
+    nvteBertAttentionF16(p.qkv.rank, p.qkv.desc, p.cu.rank, p.cu.desc, p.ctx.rank, p.ctx.desc, scale,
+                         c.heads);
+    gemm(p.ctx, wo, p.x, p.x, 0, 1.0f);  // residual: C aliases D
+    nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+    gemm(p.x, w1, p.ffn, p.ffn, 1, 0.0f);  // erf GELU
+    gemm(p.ffn, w2, p.x, p.x, 0, 1.0f);
+    nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+  }
+  return status();
+}
+
+int forward_impl(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void *mask,
+                 int64_t rankTypes, void *types, int use_graph) {
+  for (const Tensor &w : p.weights)
+    if (!w.desc) return HOM_ERR_INVALID;
+  if (!use_graph || !p.warmed_up) {
+    // The first call always runs eagerly: it performs the library's one-time set-up
+    // (kernel attributes, tensor-map cache), which must not happen during capture.
+    p.warmed_up = true;
+    return issue_forward(p, rankIds, ids, rankMask, mask, rankTypes, types);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(homGetStream());
+  void *ids_data = static_cast<void **>(ids)[1], *mask_data = static_cast<void **>(mask)[1];
+  void *types_data = static_cast<void **>(types)[1];
+  if (p.graph_exec && (ids_data != p.graph_ids || mask_data != p.graph_mask ||
+                       types_data != p.graph_types)) {
+    cudaGraphExecDestroy(p.graph_exec);
+    p.graph_exec = nullptr;
+  }
+  if (!p.graph_exec) {
+    cudaStream_t user_stream = stream;
+    if (stream == nullptr) {  // the legacy default stream cannot be captured
+      if (!p.own_stream && cudaStreamCreateWithFlags(&p.own_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return HOM_ERR_CUDA;
+      stream = p.own_stream;
+      homSetStream(stream);
+    }
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      homSetStream(user_stream);
+      return HOM_ERR_CUDA;
+    }
+    const int rc = issue_forward(p, rankIds, ids, rankMask, mask, rankTypes, types);
+    const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
+    homSetStream(user_stream);
+    if (rc != 0 || ce != cudaSuccess || !graph) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc ? rc : HOM_ERR_CUDA;
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&p.graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+      p.graph_exec = nullptr;
+      return HOM_ERR_CUDA;
+    }
+    p.graph_ids = ids_data;
+    p.graph_mask = mask_data;
+    p.graph_types = types_data;
+  }
+  return cudaGraphLaunch(p.graph_exec, static_cast<cudaStream_t>(homGetStream())) == cudaSuccess
+             ? status()
+             : HOM_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t homBertWeightCount(const HomBertConfig *cfg) { return cfg ? 3 + 4 * cfg->layers : 0; }
+
+void *homBertCreate(const HomBertConfig *cfg) {
+  if (!cfg || cfg->layers <= 0 || cfg->hidden <= 0 || cfg->heads <= 0 || cfg->ffn <= 0 ||
+      cfg->batch <= 0 || cfg->seq <= 0 || cfg->hidden % cfg->heads != 0)
+    return nullptr;
+  auto *p = new Program();
+  p->cfg = *cfg;
+  p->weights.resize(static_cast<size_t>(homBertWeightCount(cfg)));
+  const int32_t b = cfg->batch, s = cfg->seq, h = cfg->hidden;
+  p->x = from_alloc(alloc3DMemRefNVGPUF16(b, s, h));
+  p->type_rows = from_alloc(alloc3DMemRefNVGPUF16(b, s, h));
+  p->qkv = from_alloc(alloc3DMemRefNVGPUF16(b, s, 3 * h));
+  p->ctx = from_alloc(alloc3DMemRefNVGPUF16(b, s, h));
+  p->ffn = from_alloc(alloc3DMemRefNVGPUF16(b, s, cfg->ffn));
+  p->cu = from_alloc(alloc1DMemRefNVGPUI32(b + 1));
+  // int64 staging for the host entry point: 3 x [b, s] carved from one I32 allocation.
+  Tensor staging = from_alloc(alloc1DMemRefNVGPUI32(3 * 2 * b * s));
+  if (status() != 0 || !p->x.data() || !p->type_rows.data() || !p->qkv.data() || !p->ctx.data() ||
+      !p->ffn.data() || !p->cu.data() || !staging.data()) {
+    homBertDestroy(p);
+    release(staging, false);
+    return nullptr;
+  }
+  char *base = static_cast<char *>(staging.data());
+  const int64_t plane = static_cast<int64_t>(b) * s * 8;
+  p->ids_dev = make_view(base, {b, s});
+  p->mask_dev = make_view(base + plane, {b, s});
+  p->types_dev = make_view(base + 2 * plane, {b, s});
+  // ids_dev keeps the staging allocation alive and frees it.
+  p->ids_dev.owned_buffer = true;
+  std::free(staging.desc);
+  return p;
+}
+
+void homBertDestroy(void *program) {
+  auto *p = static_cast<Program *>(program);
+  if (!p) return;
+  if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
+  if (p->own_stream) cudaStreamDestroy(p->own_stream);
+  for (Tensor &w : p->weights) release(w, true);
+  release(p->x, true);
+  release(p->type_rows, true);
+  release(p->qkv, true);
+  release(p->ctx, true);
+  release(p->ffn, true);
+  release(p->cu, false);
+  release(p->mask_dev, false);
+  release(p->types_dev, false);
+  release(p->ids_dev, false);
+  delete p;
+}
+
+int homBertSetWeight(void *program, int32_t index, int64_t rank, void *descriptor) {
+  auto *p = static_cast<Program *>(program);
+  if (!p || index < 0 || index >= static_cast<int32_t>(p->weights.size()) || !descriptor ||
+      rank != 3)
+    return HOM_ERR_INVALID;
+  release(p->weights[index], true);
+  // Copy the descriptor record so the caller's may go away; the buffer stays the caller's.
+  const size_t bytes = sizeof(int64_t) * (3 + 2 * rank);
+  void *copy = std::malloc(bytes);
+  std::memcpy(copy, descriptor, bytes);
+  Tensor t;
+  t.rank = rank;
+  t.desc = copy;
+  t.owned_desc = true;
+  p->weights[index] = t;
+  if (p->graph_exec) {
+    cudaGraphExecDestroy(p->graph_exec);
+    p->graph_exec = nullptr;
+  }
+  return 0;
+}
+
+int homBertLoadConstants(void *program, int32_t first_idx) {
+  auto *p = static_cast<Program *>(program);
+  if (!p) return HOM_ERR_INVALID;
+  for (size_t i = 0; i < p->weights.size(); ++i) {
+    release(p->weights[i], true);
+    HomUnrankedMemRef m = allocConstantNVGPUF16(first_idx + static_cast<int32_t>(i));
+    if (status() != 0 || !m.descriptor) return status() ? status() : HOM_ERR_IO;
+    p->weights[i] = from_alloc(m);
+  }
+  return 0;
+}
+
+int homBertForward(void *program, int64_t rankIds, void *ids, int64_t rankMask, void *mask,
+                   int64_t rankTypes, void *types, HomUnrankedMemRef *result, int use_graph) {
+  auto *p = static_cast<Program *>(program);
+  if (!p || !ids || !mask || !types) return HOM_ERR_INVALID;
+  const int rc = forward_impl(*p, rankIds, ids, rankMask, mask, rankTypes, types, use_graph);
+  if (result) {
+    result->rank = p->x.rank;
+    result->descriptor = p->x.desc;
+  }
+  return rc;
+}
+
+int homBertForwardHost(void *program, const int64_t *ids_host, const int64_t *mask_host,
+                       const int64_t *types_host, void *out_host, int use_graph) {
+  auto *p = static_cast<Program *>(program);
+  if (!p || !ids_host || !mask_host || !types_host || !out_host) return HOM_ERR_INVALID;
+  cudaStream_t stream = static_cast<cudaStream_t>(homGetStream());
+  const size_t plane = static_cast<size_t>(p->cfg.batch) * p->cfg.seq * 8;
+  if (cudaMemcpyAsync(p->ids_dev.data(), ids_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(p->mask_dev.data(), mask_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(p->types_dev.data(), types_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+    return HOM_ERR_CUDA;
+  const int rc = forward_impl(*p, 2, p->ids_dev.desc, 2, p->mask_dev.desc, 2, p->types_dev.desc,
+                              use_graph);
+  if (rc != 0) return rc;
+  const size_t out_bytes = static_cast<size_t>(p->cfg.batch) * p->cfg.seq * p->cfg.hidden * 2;
+  if (cudaMemcpyAsync(out_host, p->x.data(), out_bytes, cudaMemcpyDeviceToHost, stream) != cudaSuccess)
+    return HOM_ERR_CUDA;
+  return homSynchronize();
+}
+
+void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d2h_bytes) {
+  auto *p = static_cast<Program *>(program);
+  if (!p) return;
+  if (h2d_bytes) *h2d_bytes = 3ll * p->cfg.batch * p->cfg.seq * 8;
+  if (d2h_bytes) *d2h_bytes = 2ll * p->cfg.batch * p->cfg.seq * p->cfg.hidden;
+}
+
+int32_t homBertLaunchesPerForward(void *program) {
+  auto *p = static_cast<Program *>(program);
+  return p ? 6 + 7 * p->cfg.layers : 0;
+}
+
+}  // extern "C"

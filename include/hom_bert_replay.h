@@ -1,0 +1,84 @@
+/* libhom_bert_replay.so: a C++ stand-in for the model library that Hands-on-MLIR compiles
+ * from BERT (`_hom_forward`, reached through `_hom_ciface_forward(void**)`,
+ * lib/Conversions/Function/UnifyLLVMFuncInterface.cpp:60-128, and driven by
+ * examples/torch/bert/bert.cu:81-125).  The MLIR toolchain that would produce the real model
+ * library is not available, so this program issues the same straight-line sequence of
+ * runner-utils calls that the lowering emits (lib/Conversions/Function/HOMNVGPUToFunc.cpp)
+ * and nothing else: every tensor operation goes through the C ABI of
+ * hom_nvgpu_runner_utils.h, buffers come from alloc3DMemRefNVGPUF16 / alloc1DMemRefNVGPUI32
+ * exactly as the hoisted init function allocates them
+ * (lib/Conversions/Function/ExtractInitFunc.cpp:94-186).
+ *
+ * Per forward: thrustCuSeqLenI64; thrustGatherF16 x2, thrustElementwiseAddF16 x2,
+ * nvteLayernormF16 (embeddings); then per encoder layer GEMM(QKV), nvteBertAttentionF16,
+ * GEMM(out, C = D = residual, beta 1), nvteLayernormF16, GEMM(FFN1, GELU),
+ * GEMM(FFN2, C = D = residual, beta 1), nvteLayernormF16.
+ *
+ * All functions return 0 on success, otherwise the runner-utils error code
+ * (homGetLastErrorString() has the text).  Nothing here has a counterpart symbol in the
+ * reference; it replaces a generated artefact.
+ */
+#ifndef HOM_BERT_REPLAY_H
+#define HOM_BERT_REPLAY_H
+
+#include <stdint.h>
+
+#include "hom_nvgpu_runner_utils.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct HomBertConfig {
+  int32_t layers;      /* 12 (base) / 24 (large) */
+  int32_t hidden;      /* 768 / 1024 */
+  int32_t heads;       /* 12 / 16 */
+  int32_t ffn;         /* 3072 / 4096 */
+  int32_t vocab;       /* 30522 */
+  int32_t type_vocab;  /* 2 */
+  int32_t batch;       /* sequences per forward on this GPU */
+  int32_t seq;
+  float eps;           /* 1e-12 */
+  int32_t weights_nk;  /* 0: weights [1,K,N] via cutlassGemmF16; 1: [1,N,K] via nvteGemmF16 */
+} HomBertConfig;
+
+/* Number of weight tensors a program with this config takes: 3 embeddings + 4 per layer.
+ * Order: 0 word_emb [1,vocab,H]; 1 pos_emb [1,seq,H] (the constant-folded position slice);
+ * 2 type_emb [1,type_vocab,H]; then per layer wqkv [1,H,3H], wo [1,H,H], w1 [1,H,F],
+ * w2 [1,F,H] (each [1,N,K] instead when weights_nk). */
+HOM_EXPORT int32_t homBertWeightCount(const HomBertConfig *cfg);
+
+/* Creates the program on the current device and allocates its activation buffers. */
+HOM_EXPORT void *homBertCreate(const HomBertConfig *cfg);
+HOM_EXPORT void homBertDestroy(void *program);
+
+/* Binds weight `index` to a caller-owned device memref (kept by reference). */
+HOM_EXPORT int homBertSetWeight(void *program, int32_t index, int64_t rank, void *descriptor);
+/* Loads every weight with allocConstantNVGPUF16(first_idx + index), as the compiled model's
+ * init function does; the program owns (and frees) those buffers. */
+HOM_EXPORT int homBertLoadConstants(void *program, int32_t first_idx);
+
+/* Enqueues one forward on the library's current stream.  ids / mask / token types are
+ * int64 [batch, seq] device memrefs; *result receives the descriptor of the program-owned
+ * final hidden states, fp16 [batch, seq, hidden].  use_graph != 0 captures the call sequence
+ * into a CUDA graph on first use (for the given input buffers) and replays it afterwards. */
+HOM_EXPORT int homBertForward(void *program, int64_t rankIds, void *ids, int64_t rankMask,
+                              void *mask, int64_t rankTypes, void *types,
+                              HomUnrankedMemRef *result, int use_graph);
+
+/* End-to-end step with HOST buffers: copies ids / mask / token types (int64 [batch, seq],
+ * ideally pinned) to the device, runs the forward, copies the fp16 [batch, seq, hidden]
+ * result to out_host and waits for it. */
+HOM_EXPORT int homBertForwardHost(void *program, const int64_t *ids_host, const int64_t *mask_host,
+                                  const int64_t *types_host, void *out_host, int use_graph);
+
+/* Bytes moved per homBertForwardHost call (host->device, device->host). */
+HOM_EXPORT void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d2h_bytes);
+/* Runner-utils calls (= kernel launches) one forward issues. */
+HOM_EXPORT int32_t homBertLaunchesPerForward(void *program);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HOM_BERT_REPLAY_H */
