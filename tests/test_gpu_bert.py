@@ -1,0 +1,132 @@
+"""End-to-end parity of the replayed BERT call sequence on the GPU against the CPU oracle's
+encoder, on the final hidden states (valid tokens), plus launch accounting, CUDA-graph
+replay, the host-buffer entry point and the constant-file initialisation path."""
+import numpy as np
+import pytest
+
+from util import assert_bits_equal, assert_end_to_end_close, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def f16(x):
+    return np.asarray(x, dtype=np.float32).astype(np.float16)
+
+
+def tiny_model(seed, L=2, H=256, heads=4, F=512, V=1000, S=128):
+    from hands_on_mlir_b200.bert_program import BertConfig
+    cfg = BertConfig(layers=L, hidden=H, heads=heads, ffn=F, vocab=V)
+    rng = np.random.Generator(np.random.PCG64(seed))
+    w = {name: f16(rng.normal(0, 0.02, cfg.weight_shape(name, S))) for name in cfg.weight_names()}
+    return cfg, w, rng
+
+
+def run_case(hom, dev, oracle, cfg, w, ids, mask, types, use_graph=False):
+    from hands_on_mlir_b200.bert_program import BertProgram
+    B, S = ids.shape
+    prog = BertProgram(cfg, B, S)
+    prog.set_weights({k: to_dev(v, dev) for k, v in w.items()})
+    tids, tmask, ttypes = to_dev(ids, dev), to_dev(mask, dev), to_dev(types, dev)
+    res = prog.forward(tids, tmask, ttypes, use_graph=use_graph)
+    got = prog.result_to_torch(res)
+    hom.synchronize()
+    return prog, got.cpu().numpy(), (tids, tmask, ttypes)
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_encoder_final_hidden_states_match_oracle(hom, cuda, oracle, seed):
+    cfg, w, rng = tiny_model(seed)
+    B, S = 4, 128
+    lens = np.array([128, 64, 100, 17])
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.int64)
+    types = rng.integers(0, 2, (B, S)).astype(np.int64)
+    before = hom.launch_count()
+    prog, got, _ = run_case(hom, cuda, oracle, cfg, w, ids, mask, types)
+    assert hom.launch_count() - before == prog.launches_per_forward() + 1  # + the read-back gather
+    want = oracle.bert_encoder(w, ids, mask, types, heads=cfg.heads, eps=cfg.eps)
+    for b, n in enumerate(lens):
+        assert_end_to_end_close(got[b, :n], want[b, :n], f"hidden states, sequence {b}")
+    prog.close()
+
+
+def test_bert_base_layer_shapes_match_oracle(hom, cuda, oracle):
+    """Two layers at BERT-base width (hidden 768, 12 heads, FFN 3072), batch 8 x seq 128,
+    attention mask all ones as in the whole-model benchmark configuration."""
+    cfg, w, rng = tiny_model(3, L=2, H=768, heads=12, F=3072, V=2000)
+    B, S = 8, 128
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = np.ones((B, S), dtype=np.int64)
+    types = np.zeros((B, S), dtype=np.int64)
+    prog, got, _ = run_case(hom, cuda, oracle, cfg, w, ids, mask, types)
+    want = oracle.bert_encoder(w, ids, mask, types, heads=cfg.heads, eps=cfg.eps)
+    assert_end_to_end_close(got, want, "bert-base-width hidden states")
+    prog.close()
+
+
+def test_graph_replay_and_host_entry_point_are_bit_identical(hom, cuda, oracle):
+    import torch
+    cfg, w, rng = tiny_model(5)
+    B, S = 2, 128
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = np.ones((B, S), dtype=np.int64)
+    types = np.zeros((B, S), dtype=np.int64)
+    prog, eager, (tids, tmask, ttypes) = run_case(hom, cuda, oracle, cfg, w, ids, mask, types)
+    for _ in range(3):  # first graph call captures, later ones replay
+        res = prog.forward(tids, tmask, ttypes, use_graph=True)
+    replay = prog.result_to_torch(res).cpu().numpy()
+    assert_bits_equal(replay, eager, "graph replay vs eager")
+    out_h = torch.empty((B, S, cfg.hidden), dtype=torch.float16).pin_memory()
+    hi, hm, ht = (torch.from_numpy(x).pin_memory() for x in (ids, mask, types))
+    for use_graph in (False, True, True):
+        out_h.zero_()
+        prog.forward_host(hi, hm, ht, out_h, use_graph=use_graph)
+        assert_bits_equal(out_h.numpy(), eager, f"host entry point (graph={use_graph})")
+    h2d, d2h = prog.host_traffic()
+    assert h2d == 3 * B * S * 8 and d2h == B * S * cfg.hidden * 2
+    prog.close()
+
+
+def test_init_from_constant_files(hom, cuda, oracle, tmp_path):
+    """Weights loaded by allocConstantNVGPUF16 from '<idx>.txt' files, as the compiled model's
+    init function does."""
+    from hands_on_mlir_b200.bert_program import BertProgram
+    cfg, w, rng = tiny_model(7, L=1, H=128, heads=2, F=256, V=40)
+    for i, name in enumerate(cfg.weight_names()):
+        arr = w[name].astype(np.float32)
+        with open(tmp_path / f"{i}.txt", "w") as f:
+            f.write(" ".join(str(d) for d in arr.shape) + "\n")
+            f.write(" ".join(repr(float(v)) for v in arr.ravel()) + "\n")
+    hom.lib.homSetConstantDir(str(tmp_path).encode())
+    B, S = 2, 128
+    prog = BertProgram(cfg, B, S)
+    prog.load_constants(0)
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = np.ones((B, S), dtype=np.int64)
+    types = np.zeros((B, S), dtype=np.int64)
+    res = prog.forward(to_dev(ids, cuda), to_dev(mask, cuda), to_dev(types, cuda))
+    got = prog.result_to_torch(res).cpu().numpy()
+    hom.synchronize()
+    want = oracle.bert_encoder(w, ids, mask, types, heads=cfg.heads, eps=cfg.eps)
+    assert_end_to_end_close(got, want, "constants-file model")
+    prog.close()
+
+
+def test_nk_weight_layout_path(hom, cuda, oracle):
+    """The TransformerEngine-style path: weights stored [1,N,K], GEMMs through nvteGemmF16."""
+    from hands_on_mlir_b200.bert_program import BertProgram
+    cfg, w, rng = tiny_model(9, L=1)
+    B, S = 2, 128
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = np.ones((B, S), dtype=np.int64)
+    types = np.zeros((B, S), dtype=np.int64)
+    prog = BertProgram(cfg, B, S, weights_nk=True)
+    wt = {k: (to_dev(np.ascontiguousarray(v.transpose(0, 2, 1)), cuda) if k[0] == "w" and "_emb" not in k
+              else to_dev(v, cuda)) for k, v in w.items()}
+    prog.set_weights(wt)
+    res = prog.forward(to_dev(ids, cuda), to_dev(mask, cuda), to_dev(types, cuda))
+    got = prog.result_to_torch(res).cpu().numpy()
+    hom.synchronize()
+    want = oracle.bert_encoder(w, ids, mask, types, heads=cfg.heads, eps=cfg.eps)
+    assert_end_to_end_close(got, want, "[N,K] weights")
+    prog.close()

@@ -34,3 +34,23 @@ def assert_bits_equal(got, want, what=""):
         i = tuple(bad[0])
         raise AssertionError(f"{what}: {len(bad)} elements differ bitwise; first at {i}: "
                              f"got {got[i]!r} want {want[i]!r}")
+
+
+def assert_end_to_end_close(got, want, what=""):
+    """End-to-end criterion for final hidden states after several layers.
+
+    rtol 1e-3 is one fp16 ulp, so two correct implementations that round an intermediate
+    differently (fp32 tensor-core accumulation here, double accumulation in the oracle) drift
+    by a few ulps after a few layers.  Required: at least 99.9 % of the elements within
+    rtol 1e-3 / atol 1e-3, and every element within the reference's own end-to-end bound
+    (abs <= 1e-2 or rel <= 1e-2, examples/torch/bert/bert.cu:148-153)."""
+    got = np.asarray(got).astype(np.float64)
+    want = np.asarray(want).astype(np.float64)
+    assert got.shape == want.shape
+    assert np.isfinite(got).all(), f"{what}: non-finite output"
+    err = np.abs(got - want)
+    tight = err <= ATOL + RTOL * np.abs(want)
+    frac = 1.0 - tight.mean()
+    assert frac <= 1e-3, f"{what}: {frac:.2%} of elements outside rtol/atol 1e-3 (max err {err.max():.3e})"
+    loose = (err <= 1e-2) | (err <= 1e-2 * np.abs(want))
+    assert loose.all(), f"{what}: max abs err {err.max():.3e} exceeds the 1e-2 end-to-end bound"
