@@ -2,7 +2,7 @@
 """Benchmark of the BERT runtime-kernel path: fp16 encoder sequences/s on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload bert-base|bert-large]
-                    [--impl reference]
+                    [--impl reference] [--op NAME [--l2-resident]]
 
 A step is one encoder forward over one batch of synthetic input (random-init weights
 N(0, 0.02), LayerNorm without affine, no biases; ids uniform in [1000, 30522)):
@@ -241,6 +241,142 @@ def reference_matmul_rate():
         return None
 
 
+
+# ------------------------------------------------------------------ op-level arm
+
+OP_CASES = {
+    # name: (kind, parameters)
+    "gemm-c1": ("gemm", dict(m=512, n=3072, k=768, act=1, c="bias")),      # GEMM+bias+GELU config
+    "gemm-qkv": ("gemm", dict(m=4096, n=2304, k=768, act=0, c=None)),
+    "gemm-out": ("gemm", dict(m=4096, n=768, k=768, act=0, c="residual")),
+    "gemm-ffn1": ("gemm", dict(m=4096, n=3072, k=768, act=1, c=None)),
+    "gemm-ffn2": ("gemm", dict(m=4096, n=768, k=3072, act=0, c="residual")),
+    "gemm-large-ffn1": ("gemm", dict(m=16384, n=4096, k=1024, act=1, c=None)),
+    "gemm-large-ffn2": ("gemm", dict(m=16384, n=1024, k=4096, act=0, c="residual")),
+    "ln-c2": ("ln", dict(rows=4096, hidden=768, residual=True, affine=True)),  # residual+LN config
+    "ln-inplace": ("ln", dict(rows=4096, hidden=768, residual=False, affine=False)),
+    "ln-large": ("ln", dict(rows=131072, hidden=1024, residual=False, affine=False)),
+    "attn-c3": ("attn", dict(bs=32, seq=128, heads=12, lens=(64, 128))),    # attention config
+    "attn-large": ("attn", dict(bs=32, seq=512, heads=16, lens=(256, 512))),
+}
+
+
+def run_op_arm(args):
+    """One kernel of the path on its own: rotating buffer sets larger than L2, CUDA events on
+    the launching stream around `steps` launches, per-launch average."""
+    import torch
+    from __graft_entry__ import load_package
+
+    pkg = load_package()
+    hom = pkg.runner()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    hom.use_torch_stream()
+    kind, prm = OP_CASES[args.op]
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    randn = lambda *shape, std=1.0: (torch.randn(shape, generator=g, device=dev) * std).half()
+    peaks, peak_src = load_peaks()
+    sets, launch = [], None
+    if kind == "gemm":
+        if args.shape:
+            prm = dict(prm)
+            prm["m"], prm["n"], prm["k"] = (int(v) for v in args.shape.split(","))
+        m, n, k = prm["m"], prm["n"], prm["k"]
+        per_set = 2 * (m * k + k * n + m * n)
+        nsets = max(2, min(16, -(-300_000_000 // per_set))) if not args.l2_resident else 1
+        for _ in range(nsets):
+            A = (torch.rand((1, m, k), generator=g, device=dev) * 2 - 1).half()
+            B = randn(1, k, n, std=0.02)
+            D = randn(1, m, n) if prm["c"] == "residual" else torch.empty((1, m, n), dtype=torch.float16, device=dev)
+            C = (torch.rand((1, 1, n), generator=g, device=dev) * 2 - 1).half() if prm["c"] == "bias" else D
+            sets.append((A, B, C, D))
+        beta = 1.0 if prm["c"] else 0.0
+        launch = lambda s: hom.cutlassGemmF16(s[0], s[1], s[2], s[3], activation=prm["act"], beta=beta,
+                                              gemmNum=args.tile)
+        flops = 2.0 * m * n * k
+        nbytes = per_set + (2 * m * n if prm["c"] == "residual" else 2 * n if prm["c"] else 0)
+        bound, work, unit, peak = "tensor", flops, "TFLOP/s", peaks["bf16_tflops"]
+        peak_note = f"{peak_src} (burst dense bf16/fp16; kernel timed alone)"
+        desc = f"GEMM {m}x{n}x{k} act={prm['act']} C={prm['c']} tile={hom.gemm_query_tile(m, n, k, prm['act'])}"
+    elif kind == "ln":
+        rows, hidden = prm["rows"], prm["hidden"]
+        per_set = 2 * rows * hidden * (3 if prm["residual"] else 2)
+        nsets = max(2, min(32, -(-300_000_000 // per_set))) if not args.l2_resident else 1
+        gamma = (1 + torch.randn(hidden, generator=g, device=dev) * 0.1).half()
+        beta_t = (torch.randn(hidden, generator=g, device=dev) * 0.1).half()
+        for _ in range(nsets):
+            X = randn(rows, hidden)
+            R = randn(rows, hidden) if prm["residual"] else None
+            O = torch.empty_like(X) if prm["residual"] else X
+            sets.append((X, R, O))
+        if prm["residual"]:
+            launch = lambda s: hom.homResidualLayernormF16(s[0], s[1], gamma, beta_t, s[2], 1e-12)
+        else:
+            launch = lambda s: hom.nvteLayernormF16(s[0], 1e-12)
+        nbytes = per_set + (4 * hidden if prm["affine"] else 0)
+        bound, work, unit, peak = "hbm", float(nbytes), "GB/s", peaks["hbm_gbs"]
+        peak_note = f"{peak_src} (HBM copy)"
+        desc = f"LayerNorm rows={rows} hidden={hidden} residual={prm['residual']} affine={prm['affine']}"
+    else:
+        bs, seq, heads = prm["bs"], prm["seq"], prm["heads"]
+        rng = np.random.Generator(np.random.PCG64(0))
+        lens = rng.integers(prm["lens"][0], prm["lens"][1] + 1, bs)
+        cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(dev)
+        per_set = 2 * bs * seq * heads * 64 * 4
+        nsets = max(2, min(16, -(-300_000_000 // per_set))) if not args.l2_resident else 1
+        for _ in range(nsets):
+            sets.append((randn(bs, seq, 3 * heads * 64), torch.empty((bs, seq, heads * 64), dtype=torch.float16, device=dev)))
+        launch = lambda s: hom.nvteBertAttentionF16(s[0], cu, s[1], 0.125, heads)
+        nbytes = per_set + 4 * (bs + 1)
+        flops = 4.0 * 64 * heads * float((lens.astype(np.float64) ** 2).sum())
+        bound, work, unit, peak = "hbm", float(nbytes), "GB/s", peaks["hbm_gbs"]
+        peak_note = f"{peak_src} (HBM copy)"
+        desc = f"attention bs={bs} seq={seq} heads={heads} valid lengths U{prm['lens']}"
+
+    for i in range(max(args.warmup, 3)):
+        launch(sets[i % len(sets)])
+    hom.synchronize()
+    # One pass over the buffer sets is captured into a CUDA graph so that short kernels are
+    # not limited by the Python call overhead; `steps` launches = steps / len(sets) replays.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for st in sets:
+            launch(st)
+    replays = max(1, args.steps // len(sets))
+    args.steps = replays * len(sets)
+    graph.replay()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        ev0.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        ev1.record(stream)
+        torch.cuda.synchronize()
+    hom.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    achieved = work / (ms / 1e3) / (1e12 if bound == "tensor" else 1e9)
+    line = {
+        "metric": f"{args.op}_{'tflops' if bound == 'tensor' else 'gbs'}", "value": achieved,
+        "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": desc,
+                   "l2": ("single buffer set, L2 resident" if args.l2_resident else
+                          f"{len(sets)} rotating buffer sets, {len(sets) * per_set / 1e6:.0f} MB > 126 MB L2")},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                     "frac": achieved / peak, "peak_source": peak_note, "traffic": None,
+                     "algorithmic_bytes": nbytes,
+                     "algorithmic_flops": flops if kind != "ln" else 0.0},
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 # ------------------------------------------------------------------------- GPU arm
 
 def run_gpu_arm(args, cfg, workload):
@@ -425,7 +561,17 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bert-base")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--op", choices=sorted(OP_CASES), default=None,
+                    help="time one kernel of the path on its own instead of the whole encoder")
+    ap.add_argument("--tile", type=int, default=0,
+                    help="with --op gemm-*: force tile-table row 1..4 (0 = automatic)")
+    ap.add_argument("--shape", default=None, help="with --op gemm-*: override M,N,K")
+    ap.add_argument("--l2-resident", action="store_true",
+                    help="with --op: reuse one buffer set (L2-resident figure)")
     args = ap.parse_args()
+    if args.op:
+        run_op_arm(args)
+        return
 
     from __graft_entry__ import load_package
     load_package()

@@ -204,8 +204,9 @@ class RunnerUtils:
                    gemmNum, splitKFactor)
 
     def nvteGemmF16(self, A, B, C, D, activation=0, alpha=1.0, beta=0.0, transa=False,
-                    transb=True):
-        self._gemm(self.lib.nvteGemmF16, A, B, C, D, transa, transb, activation, alpha, beta, 0, 0)
+                    transb=True, gemmNum=0):
+        self._gemm(self.lib.nvteGemmF16, A, B, C, D, transa, transb, activation, alpha, beta,
+                   gemmNum, 0)
 
     def nvteLayernormF16(self, A, eps=1e-6):
         self.lib.nvteLayernormF16(*_as_args(A), eps)

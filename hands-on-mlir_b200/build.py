@@ -32,6 +32,7 @@ REPLAY_LIB = LIB_DIR / "libhom_bert_replay.so"
 RUNNER_SOURCES = [
     "context.cu",
     "gemm_sm100.cu",
+    "gemm_pair_sm100.cu",
     "attention_sm100.cu",
     "bandwidth_kernels.cu",
     "runner_utils.cu",

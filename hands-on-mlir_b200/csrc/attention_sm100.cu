@@ -49,12 +49,14 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
+  pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
   const int hidden = p.heads * kHeadDim;
   const int q0 = q_tile * kTile;
 
+  pdl_wait();  // cu_seqlens and the packed QKV come from earlier kernels of the stream
   int len = p.cu_seqlens[batch + 1] - p.cu_seqlens[batch];
   len = max(0, min(len, p.seq));
 
@@ -307,8 +309,8 @@ bool run(const Problem &pb, cudaStream_t stream) {
   const double flops = 4.0 * d * pb.heads * pb.bs * static_cast<double>(pb.seq) * pb.seq;
   const double bytes = 2.0 * rows * cols + 2.0 * rows * pb.heads * d + 4.0 * (pb.bs + 1);
   LaunchScope scope(kOpAttention, flops, bytes);
-  attention_f16_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm, p);
-  return check_cuda(cudaGetLastError(), "attention kernel launch");
+  return check_cuda(launch_pdl(attention_f16_kernel, grid, dim3(kThreads), kSmemBytes, stream, 1, tm, p),
+                    "attention kernel launch");
 }
 
 }  // namespace attention

@@ -6,6 +6,7 @@
 // They replace TransformerEngine's LayerNorm (include/NVGPUKernels/Layernorm.h:584-694) and
 // the Thrust pipelines of include/NVGPUKernels/{ElementwiseRunner,GatherRunner,CuSeqLen}.h.
 #include "bandwidth_kernels.cuh"
+#include "ptx_sm100.cuh"
 
 namespace hom {
 namespace bw {
@@ -25,9 +26,11 @@ __device__ __forceinline__ float warp_sum(float v) {
 // variance taken around the mean (two passes over registers).
 template <int VPT>
 __global__ void __launch_bounds__(128)
-layernorm_f16_warp_kernel(const __half *__restrict__ x, const __half *__restrict__ res,
-                          const __half *__restrict__ gamma, const __half *__restrict__ beta,
-                          __half *__restrict__ out, long long rows, int hidden, float eps) {
+layernorm_f16_warp_kernel(const __half *x, const __half *res,
+                          const __half *gamma, const __half *beta,
+                          __half *out, long long rows, int hidden, float eps) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -122,9 +125,11 @@ layernorm_f16_warp_kernel(const __half *__restrict__ x, const __half *__restrict
 // the row is re-read for each pass.
 template <typename T>
 __global__ void __launch_bounds__(128)
-layernorm_generic_kernel(const T *__restrict__ x, const T *__restrict__ res,
-                         const T *__restrict__ gamma, const T *__restrict__ beta,
-                         T *__restrict__ out, long long rows, int hidden, float eps) {
+layernorm_generic_kernel(const T *x, const T *res,
+                         const T *gamma, const T *beta,
+                         T *out, long long rows, int hidden, float eps) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -183,8 +188,10 @@ __device__ __forceinline__ float apply_f(float a, float b) {
 // out[i] = a[i] op b[i % period] on 16-byte vectors (period counted in vectors).
 template <int OP>
 __global__ void __launch_bounds__(256)
-elementwise_f16_vec_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b,
-                           uint4 *__restrict__ out, long long nvec, long long period) {
+elementwise_f16_vec_kernel(const uint4 *a, const uint4 *b,
+                           uint4 *out, long long nvec, long long period) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
        i += stride) {
@@ -202,8 +209,10 @@ elementwise_f16_vec_kernel(const uint4 *__restrict__ a, const uint4 *__restrict_
 
 template <int OP>
 __global__ void __launch_bounds__(256)
-elementwise_f32_vec_kernel(const float4 *__restrict__ a, const float4 *__restrict__ b,
-                           float4 *__restrict__ out, long long nvec, long long period) {
+elementwise_f32_vec_kernel(const float4 *a, const float4 *b,
+                           float4 *out, long long nvec, long long period) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
        i += stride) {
@@ -223,8 +232,10 @@ elementwise_f32_vec_kernel(const float4 *__restrict__ a, const float4 *__restric
 // (ElementwiseRunner.h:101-113).
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
-elementwise_generic_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ out,
+elementwise_generic_kernel(const T *a, const T *b, T *out,
                            long long n, BroadcastShape sh) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += stride) {
@@ -251,6 +262,8 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const long long *__restrict__ idx, const T *__restrict__ table,
                    T *__restrict__ out, long long rows, long long vocab, int hidden,
                    int vec_per_row) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -273,6 +286,8 @@ gather_rows_kernel(const long long *__restrict__ idx, const T *__restrict__ tabl
 template <typename T>
 __global__ void __launch_bounds__(1024)
 cu_seqlen_kernel(const T *__restrict__ mask, int *__restrict__ out, int bs, int seq) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
   __shared__ int warp_tot[32];
   __shared__ int carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -342,12 +357,13 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
   const bool vec_ok = hidden % 8 == 0 && hidden <= 32 * 8 * 16 && aligned16(x) && aligned16(out) &&
                       (!res || aligned16(res)) && (!gamma || aligned16(gamma)) &&
                       (!beta || aligned16(beta));
+  cudaError_t err = cudaSuccess;
   if (vec_ok) {
     const int nvec = static_cast<int>(hidden / 8);
     const int vpt = (nvec + 31) / 32;
 #define HOM_LN_CASE(V)                                                                            \
-  layernorm_f16_warp_kernel<V><<<blocks, 128, 0, stream>>>(x, res, gamma, beta, out, rows,       \
-                                                           static_cast<int>(hidden), eps)
+  err = launch_pdl(layernorm_f16_warp_kernel<V>, dim3(blocks), dim3(128), 0, stream, 1, x, res,   \
+                   gamma, beta, out, static_cast<long long>(rows), static_cast<int>(hidden), eps)
     if (vpt <= 1) HOM_LN_CASE(1);
     else if (vpt == 2) HOM_LN_CASE(2);
     else if (vpt == 3) HOM_LN_CASE(3);
@@ -356,10 +372,11 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
     else HOM_LN_CASE(16);
 #undef HOM_LN_CASE
   } else {
-    layernorm_generic_kernel<__half><<<blocks, 128, 0, stream>>>(x, res, gamma, beta, out, rows,
-                                                                 static_cast<int>(hidden), eps);
+    err = launch_pdl(layernorm_generic_kernel<__half>, dim3(blocks), dim3(128), 0, stream, 1, x, res,
+                     gamma, beta, out, static_cast<long long>(rows), static_cast<int>(hidden), eps);
   }
-  return check_cuda(cudaGetLastError(), "layernorm kernel launch");
+  return check_cuda(err, "layernorm kernel launch") &&
+         check_cuda(cudaGetLastError(), "layernorm kernel launch");
 }
 
 bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, float eps,
@@ -367,9 +384,11 @@ bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, flo
   if (rows == 0 || hidden == 0) return true;
   LaunchScope scope(kOpLayernorm, 0.0, 8.0 * rows * hidden);
   const unsigned blocks = static_cast<unsigned>((rows + 3) / 4);
-  layernorm_generic_kernel<float><<<blocks, 128, 0, stream>>>(x, nullptr, nullptr, nullptr, out,
-                                                              rows, static_cast<int>(hidden), eps);
-  return check_cuda(cudaGetLastError(), "layernorm kernel launch");
+  const float *none = nullptr;
+  return check_cuda(launch_pdl(layernorm_generic_kernel<float>, dim3(blocks), dim3(128), 0, stream, 1,
+                               x, none, none, none, out, static_cast<long long>(rows),
+                               static_cast<int>(hidden), eps),
+                    "layernorm kernel launch");
 }
 
 template <int OP>
@@ -380,29 +399,30 @@ static bool elementwise_dispatch(bool is_f16, const void *a, const void *b, void
   const bool periodic = b_period > 0;
   const bool vec_ok = periodic && n % vec_elems == 0 && b_period % vec_elems == 0 && aligned16(a) &&
                       aligned16(b) && aligned16(out);
+  cudaError_t err = cudaSuccess;
   if (vec_ok) {
     const long long nvec = n / vec_elems, pvec = b_period / vec_elems;
     const int grid = grid_for(nvec, 256);
     if (is_f16)
-      elementwise_f16_vec_kernel<OP><<<grid, 256, 0, stream>>>(
-          static_cast<const uint4 *>(a), static_cast<const uint4 *>(b), static_cast<uint4 *>(out),
-          nvec, pvec);
+      err = launch_pdl(elementwise_f16_vec_kernel<OP>, dim3(grid), dim3(256), 0, stream, 1,
+                       static_cast<const uint4 *>(a), static_cast<const uint4 *>(b),
+                       static_cast<uint4 *>(out), nvec, pvec);
     else
-      elementwise_f32_vec_kernel<OP><<<grid, 256, 0, stream>>>(
-          static_cast<const float4 *>(a), static_cast<const float4 *>(b),
-          static_cast<float4 *>(out), nvec, pvec);
+      err = launch_pdl(elementwise_f32_vec_kernel<OP>, dim3(grid), dim3(256), 0, stream, 1,
+                       static_cast<const float4 *>(a), static_cast<const float4 *>(b),
+                       static_cast<float4 *>(out), nvec, pvec);
   } else {
     const int grid = grid_for(n, 256);
     if (is_f16)
-      elementwise_generic_kernel<__half, OP><<<grid, 256, 0, stream>>>(
-          static_cast<const __half *>(a), static_cast<const __half *>(b),
-          static_cast<__half *>(out), n, sh);
+      err = launch_pdl(elementwise_generic_kernel<__half, OP>, dim3(grid), dim3(256), 0, stream, 1,
+                       static_cast<const __half *>(a), static_cast<const __half *>(b),
+                       static_cast<__half *>(out), static_cast<long long>(n), sh);
     else
-      elementwise_generic_kernel<float, OP><<<grid, 256, 0, stream>>>(
-          static_cast<const float *>(a), static_cast<const float *>(b), static_cast<float *>(out),
-          n, sh);
+      err = launch_pdl(elementwise_generic_kernel<float, OP>, dim3(grid), dim3(256), 0, stream, 1,
+                       static_cast<const float *>(a), static_cast<const float *>(b),
+                       static_cast<float *>(out), static_cast<long long>(n), sh);
   }
-  return check_cuda(cudaGetLastError(), "elementwise kernel launch");
+  return check_cuda(err, "elementwise kernel launch");
 }
 
 bool elementwise(int op, bool is_f16, const void *a, const void *b, void *out, int64_t n,
@@ -430,27 +450,32 @@ bool gather_rows(bool is_f16, const int64_t *idx, const void *table, void *out, 
                       : 0;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   const long long *idx_ll = reinterpret_cast<const long long *>(idx);
+  cudaError_t err;
   if (is_f16)
-    gather_rows_kernel<__half><<<blocks, 256, 0, stream>>>(
-        idx_ll, static_cast<const __half *>(table), static_cast<__half *>(out), rows, vocab,
-        static_cast<int>(hidden), vec);
+    err = launch_pdl(gather_rows_kernel<__half>, dim3(blocks), dim3(256), 0, stream, 1, idx_ll,
+                     static_cast<const __half *>(table), static_cast<__half *>(out),
+                     static_cast<long long>(rows), static_cast<long long>(vocab),
+                     static_cast<int>(hidden), vec);
   else
-    gather_rows_kernel<float><<<blocks, 256, 0, stream>>>(
-        idx_ll, static_cast<const float *>(table), static_cast<float *>(out), rows, vocab,
-        static_cast<int>(hidden), vec);
-  return check_cuda(cudaGetLastError(), "gather kernel launch");
+    err = launch_pdl(gather_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, idx_ll,
+                     static_cast<const float *>(table), static_cast<float *>(out),
+                     static_cast<long long>(rows), static_cast<long long>(vocab),
+                     static_cast<int>(hidden), vec);
+  return check_cuda(err, "gather kernel launch");
 }
 
 bool cu_seqlen(bool is_i64, const void *mask, int *out, int64_t bs, int64_t seq,
                cudaStream_t stream) {
   LaunchScope scope(kOpCuSeqLen, 0.0, (is_i64 ? 8.0 : 4.0) * bs * seq + 4.0 * (bs + 1));
+  cudaError_t err;
   if (is_i64)
-    cu_seqlen_kernel<long long><<<1, 1024, 0, stream>>>(static_cast<const long long *>(mask), out,
-                                                        static_cast<int>(bs), static_cast<int>(seq));
+    err = launch_pdl(cu_seqlen_kernel<long long>, dim3(1), dim3(1024), 0, stream, 1,
+                     static_cast<const long long *>(mask), out, static_cast<int>(bs),
+                     static_cast<int>(seq));
   else
-    cu_seqlen_kernel<int><<<1, 1024, 0, stream>>>(static_cast<const int *>(mask), out,
-                                                  static_cast<int>(bs), static_cast<int>(seq));
-  return check_cuda(cudaGetLastError(), "cu_seqlen kernel launch");
+    err = launch_pdl(cu_seqlen_kernel<int>, dim3(1), dim3(1024), 0, stream, 1,
+                     static_cast<const int *>(mask), out, static_cast<int>(bs), static_cast<int>(seq));
+  return check_cuda(err, "cu_seqlen kernel launch");
 }
 
 }  // namespace bw

@@ -2,6 +2,7 @@
 // per-launch event timing.  The reference has none of this: it aborts the process on any
 // CUDA error (include/NVGPUKernels/Utils.h:45-52) and always uses the null stream.
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -76,6 +77,11 @@ bool check_cuda(cudaError_t e, const char *what) {
 }
 
 cudaStream_t current_stream() { return tl_stream; }
+
+bool pdl_enabled() {
+  static const bool on = std::getenv("HOM_DISABLE_PDL") == nullptr;
+  return on;
+}
 
 int *device_status_word() { return device_state().status_dev; }
 

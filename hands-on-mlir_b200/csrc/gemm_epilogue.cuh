@@ -1,0 +1,174 @@
+// Epilogue arithmetic shared by the GEMM kernels: v = alpha * acc + beta * C, optional erf
+// GELU, one rounding to fp16, 128-bit stores.  Everything is evaluated in fp32, like the
+// reference's CUTLASS LinearCombination[GELU] epilogue with a float compute type
+// (python/hom_manifest.py:43-47).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#include "ptx_sm100.cuh"
+
+namespace hom {
+namespace gemm {
+
+struct EpilogueParams {
+  const __half *C;
+  long long ldc;
+  int c_mode;  // 0: no C, 1: C is [M, N] (may alias D), 2: C is a length-N row broadcast
+  __half *D;
+  long long ldd;
+  float alpha, beta;
+  int act;  // 1: erf GELU
+  int M, N;
+};
+
+// GELU(x) = x * Phi(x) with erf from the rational-times-exponential form
+//   erfc(z) ~ (a1 t + a2 t^2 + a3 t^3 + a4 t^4 + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z >= 0
+// (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7), so that
+//   GELU(x) = x/2 + |x| * (1/2 - erfc(|x|/sqrt2)/2).
+// Two special-function-unit operations and ten FMA-class operations per element; the
+// absolute error of the result stays below 1e-6 for all x, far inside one fp16 ulp.
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+  const float az = fabsf(x) * 0.70710678118654752f;
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, az, 1.0f)));
+  // coefficients already halved: q = erfc(z) / (2 exp(-z^2))
+  float q = 0.5307027145f;
+  q = fmaf(q, t, -0.7265760135f);
+  q = fmaf(q, t, 0.7107068705f);
+  q = fmaf(q, t, -0.142248368f);
+  q = fmaf(q, t, 0.127414796f);
+  q *= t;
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(az * az * -1.4426950408889634f));
+  const float g = fmaf(-q, e, 0.5f);  // 1/2 - erfc/2
+  return fmaf(fabsf(x), g, 0.5f * x);
+}
+
+// One output row segment of 32 columns held by one thread: `acc` are the raw fp32
+// accumulator bits read from tensor memory.  Columns at or beyond N are not touched
+// (N is a multiple of 8, so whole 8-column groups are either valid or not).
+__device__ __forceinline__ void epilogue_store_32(const EpilogueParams &ep, const uint32_t (&acc)[32],
+                                                  int row, int col0) {
+  if (row >= ep.M || col0 >= ep.N) return;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = ep.alpha * __uint_as_float(acc[i]);
+  const int ncols = min(32, ep.N - col0);
+  if (ep.c_mode != 0) {
+    const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + col0 : ep.C + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(cp + g * 8);
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h2[j]);
+          v[g * 8 + 2 * j] = fmaf(ep.beta, f.x, v[g * 8 + 2 * j]);
+          v[g * 8 + 2 * j + 1] = fmaf(ep.beta, f.y, v[g * 8 + 2 * j + 1]);
+        }
+      }
+    }
+  }
+  if (ep.act == 1) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = gelu_erf_fast(v[i]);
+  }
+  __half *dp = ep.D + static_cast<long long>(row) * ep.ldd + col0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (g * 8 < ncols) {
+      uint4 out;
+      __half2 *o2 = reinterpret_cast<__half2 *>(&out);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o2[j] = __floats2half2_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+      *reinterpret_cast<uint4 *>(dp + g * 8) = out;
+    }
+  }
+}
+
+// Bytes of shared-memory staging each epilogue warp owns: 32 rows x 64 fp16 columns.
+constexpr uint32_t kEpilogueStageBytes = 32 * 128;
+
+// One warp drains a [32 rows x NCOLS] block of an accumulator: thread `lane` owns output row
+// `row0 + lane`.  Per 64-column step the warp reads the accumulator (two tcgen05.ld issued
+// back to back), applies the epilogue in fp32, writes the fp16 results into its 128-byte-
+// swizzled staging tile and lets one lane hand the tile to TMA, which writes full 128-byte
+// rows to global memory and clips rows >= M and columns >= N.  `tmem_addr` already selects
+// the warp's lane quarter and the block's first column.  After the last accumulator read the
+// function calls `release()` (the accumulator may be overwritten) while the stores drain.
+template <int NCOLS, typename Release>
+__device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
+                                                    uint32_t tmem_addr, int row0, int col0,
+                                                    uint32_t stage_smem, int lane, Release release) {
+  using namespace hom::ptx;
+  const int row = row0 + lane;
+  const bool row_ok = row < ep.M;
+  const uint32_t my_row = stage_smem + lane * 128;
+#pragma unroll 1
+  for (int step = 0; step < NCOLS / 64; ++step) {
+    const int c0 = col0 + step * 64;
+    uint32_t acc[2][32];
+    tmem_ld_32x32(tmem_addr + step * 64, acc[0]);
+    tmem_ld_32x32(tmem_addr + step * 64 + 32, acc[1]);
+    // Residual / bias values for this row segment, requested before the accumulator wait.
+    uint4 cval[8];
+    if (ep.c_mode != 0) {
+      const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const bool ok = (ep.c_mode == 2 || row_ok) && c0 + g * 8 < ep.N;
+        cval[g] = ok ? *reinterpret_cast<const uint4 *>(cp + g * 8) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    tmem_ld_wait();
+    if (step == NCOLS / 64 - 1) {
+      tc_fence_before_sync();
+      __syncwarp();
+      release();
+    }
+    // The staging tile may be rewritten once the previous store has read it.
+    if (lane == 0) bulk_wait_group_read_0();
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = ep.alpha * __uint_as_float(acc[g >> 2][(g & 3) * 8 + j]);
+      if (ep.c_mode != 0) {
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[g]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h2[j]);
+          v[2 * j] = fmaf(ep.beta, f.x, v[2 * j]);
+          v[2 * j + 1] = fmaf(ep.beta, f.y, v[2 * j + 1]);
+        }
+      }
+      if (ep.act == 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = gelu_erf_fast(v[j]);
+      }
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t *>(&h);
+      }
+      const uint32_t addr = my_row + ((static_cast<uint32_t>(g) ^ (lane & 7u)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                   "r"(w[2]), "r"(w[3])
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && c0 < ep.N && row0 < ep.M) {
+      tma_store_2d(tmD, stage_smem, c0, row0);
+      bulk_commit_group();
+    }
+  }
+}
+
+}  // namespace gemm
+}  // namespace hom

@@ -7,16 +7,19 @@
 //   warp 1    one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
 //             accumulators and releases stages / publishes accumulators with tcgen05.commit;
 //   warps 2-5 epilogue: tcgen05.ld the finished accumulator (one output row per thread,
-//             32 columns at a time), fp32 alpha/beta/bias/erf-GELU, one fp16 rounding,
-//             128-bit stores, while warp 1 already fills the other accumulator.
+//             64 columns at a time), fp32 alpha/beta/bias/erf-GELU, one fp16 rounding, results
+//             staged in swizzled shared memory and written out by TMA stores, while warp 1
+//             already fills the other accumulator.
 //
 // This replaces the reference's CUTLASS 2.x mma.sync kernels and its compile-time autotuner
 // (include/NVGPUKernels/GemmRunner.h:119-310, lib/NVGPUKernels/GemmProfiler.cu:143-236) with a
 // small per-shape tile table.
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
 
+#include "gemm_epilogue.cuh"
 #include "gemm_sm100.cuh"
 #include "ptx_sm100.cuh"
 
@@ -39,26 +42,20 @@ struct TileCfg {
   // As many stages as fit in ~196 KB.
   static constexpr int kStages = BN == 256 ? 4 : BN == 192 ? 5 : BN == 128 ? 6 : 8;
   static constexpr uint32_t kTmemCols = BN == 64 ? 128 : BN == 128 ? 256 : 512;
+  static constexpr uint32_t kStagingBytes = 4 * kEpilogueStageBytes;  // one tile per epilogue warp
   static constexpr uint32_t kBarrierBytes = 8 * (2 * kStages + 4) + 16;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
 
 struct Params {
-  int M, N, K;
-  const __half *C;
-  long long ldc;
-  int c_mode;  // 0: no C, 1: C is [M, N] (may alias D), 2: C is a length-N row broadcast
-  __half *D;
-  long long ldd;
-  float alpha, beta;
-  int act;  // 1: erf GELU
+  EpilogueParams ep;
+  int K;
   int n_blocks, num_tiles, num_kb;
+  int stages;  // ring slots in use, <= TileCfg::kStages
+  int b_grouped;  // B [K,N] is fetched through the grouped 3-D tensor map (N % 64 == 0)
   int *status;
+  long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
 };
-
-__device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
-}
 
 // Wait that ignores the CTA abort flag; used only to let in-flight TMA land before exit.
 __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
@@ -71,26 +68,30 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
 template <int BN, bool B_NK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const Params p) {
+                const __grid_constant__ CUtensorMap tmD, const Params p) {
   using Cfg = TileCfg<BN>;
-  constexpr int STAGES = Cfg::kStages;
+  constexpr int STAGES = Cfg::kStages;  // ring slots laid out in shared memory
+  const int stages_used = p.stages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
-  const uint32_t bar_base = smem_base + STAGES * Cfg::kStageBytes;
+  const uint32_t staging_base = smem_base + STAGES * Cfg::kStageBytes;
+  const uint32_t bar_base = staging_base + Cfg::kStagingBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   volatile uint32_t *tmem_slot =
-      reinterpret_cast<volatile uint32_t *>(smem_gen + STAGES * Cfg::kStageBytes + 8 * (2 * STAGES + 4));
+      reinterpret_cast<volatile uint32_t *>(smem_gen + STAGES * Cfg::kStageBytes + Cfg::kStagingBytes +
+                                            8 * (2 * STAGES + 4));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -120,36 +121,62 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int s = 0;
       uint32_t ph = 0, armed = 0;
       bool ok = true;
+      long long t_wait = 0, t_begin = clock64();
+      auto load_b = [&](int slot, int kb, int n0) {
+        const uint32_t b_dst = smem_base + slot * Cfg::kStageBytes + kABytes;
+        if (B_NK) {
+          tma_load_2d(b_dst, &tmB, full_bar(slot), kb * BK, n0);
+        } else if (p.b_grouped) {
+          tma_load_3d(b_dst, &tmB, full_bar(slot), 0, kb * BK, n0 / 64);
+        } else {
+#pragma unroll
+          for (int g = 0; g < BN / 64; ++g)
+            tma_load_2d(b_dst + g * (BK * 128), &tmB, full_bar(slot), n0 + g * 64, kb * BK);
+        }
+      };
+      // B holds weights, which no earlier kernel of the stream writes: the first ring of B
+      // tiles is requested before waiting for the previous kernel, A only after.
+      int pre = 0;
+      if (blockIdx.x < p.num_tiles) {
+        const int n0 = (blockIdx.x % p.n_blocks) * BN;
+        pre = p.num_kb < stages_used ? p.num_kb : stages_used;
+        for (int kb = 0; kb < pre; ++kb) {
+          mbar_arrive_expect_tx(full_bar(kb), Cfg::kStageBytes);
+          load_b(kb, kb, n0);
+        }
+      }
+      pdl_wait();
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / p.n_blocks) * BM;
         const int n0 = (tile % p.n_blocks) * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutProducer)) {
-            ok = false;
-            break;
+          const bool b_done = tile == static_cast<int>(blockIdx.x) && kb < pre;
+          if (!b_done) {
+            const long long tw = p.prof ? clock64() : 0;
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutProducer)) {
+              ok = false;
+              break;
+            }
+            if (p.prof) t_wait += clock64() - tw;
+            mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
+            load_b(s, kb, n0);
           }
-          mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
-          const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
-          const uint32_t b_dst = a_dst + kABytes;
-          tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, m0);
-          if (B_NK) {
-            tma_load_2d(b_dst, &tmB, full_bar(s), kb * BK, n0);
-          } else {
-#pragma unroll
-            for (int g = 0; g < BN / 64; ++g)
-              tma_load_2d(b_dst + g * (BK * 128), &tmB, full_bar(s), n0 + g * 64, kb * BK);
-          }
+          tma_load_2d(smem_base + s * Cfg::kStageBytes, &tmA, full_bar(s), kb * BK, m0);
           ++armed;
-          if (++s == STAGES) {
+          if (++s == stages_used) {
             s = 0;
             ph ^= 1u;
           }
         }
       }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[0] = clock64() - t_begin;
+        p.prof[1] = t_wait;
+      }
       if (!ok) {
         // Let every copy this thread started land before the CTA gives its shared memory back.
-        for (int st = 0; st < STAGES; ++st) {
-          const uint32_t n_st = armed / STAGES + (static_cast<uint32_t>(st) < armed % STAGES ? 1u : 0u);
+        for (int st = 0; st < stages_used; ++st) {
+          const uint32_t n_st = armed / stages_used + (static_cast<uint32_t>(st) < armed % stages_used ? 1u : 0u);
           if (n_st > 0) mbar_wait_drain(full_bar(st), (n_st - 1u) & 1u);
         }
       }
@@ -162,104 +189,85 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
+      long long t_full = 0, t_acc = 0, t_begin = clock64();
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
+        const long long ta = p.prof ? clock64() : 0;
         if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma)) break;
+        if (p.prof) t_acc += clock64() - ta;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        bool have = false;  // full[s] already seen complete by the probe of the previous block
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma)) {
-            ok = false;
-            break;
+          if (!have) {
+            const long long tw = p.prof ? clock64() : 0;
+            if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma)) {
+              ok = false;
+              break;
+            }
+            if (p.prof) t_full += clock64() - tw;
           }
+          have = false;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + kABytes;
+          const int s_next = s + 1 == stages_used ? 0 : s + 1;
+          const uint32_t ph_next = s_next == 0 ? ph ^ 1u : ph;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // A: K-major rows of 128 B; 8-row groups 1024 B apart; 16 K elements = 32 B.
             const uint64_t da = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             // B as [N,K]: same as A.  B as [K,N] (N contiguous): 64-column groups are
-            // separate TMA boxes BK*128 B apart, 8-row K groups 1024 B apart, and 16 K rows
+            // separate sub-tiles BK*128 B apart, 8-row K groups 1024 B apart, and 16 K rows
             // = 2048 B.
             const uint64_t db = B_NK ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                      : make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024);
             tc_mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            // Probe the next stage while the tensor pipe is busy with what was just queued.
+            if (k == 1 && kb + 1 < p.num_kb) have = mbar_test_wait(full_bar(s_next), ph_next);
           }
           tc_commit(empty_bar(s));
-          if (++s == STAGES) {
-            s = 0;
-            ph ^= 1u;
-          }
+          s = s_next;
+          ph = ph_next;
         }
         if (ok) tc_commit(tfull_bar(acc));
+      }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[2] = clock64() - t_begin;
+        p.prof[3] = t_full;
+        p.prof[4] = t_acc;
       }
     }
   } else {
     // --------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
     int it = 0;
+    long long t_wait = 0, t_begin = clock64();
+    pdl_wait();  // C may be produced, and D still read, by the previous kernel
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
+      const long long tw = p.prof ? clock64() : 0;
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (p.prof) t_wait += clock64() - tw;
       tc_fence_after_sync();
       const int m0 = (tile / p.n_blocks) * BM;
       const int n0 = (tile % p.n_blocks) * BN;
-      const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(r[i]);
-          const int ncols = min(32, p.N - col0);  // multiple of 8 (N % 8 == 0)
-          if (p.c_mode != 0) {
-            const __half *cp = p.c_mode == 1 ? p.C + static_cast<long long>(row) * p.ldc + col0
-                                             : p.C + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (g * 8 < ncols) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(cp + g * 8);
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 f = __half22float2(h2[j]);
-                  v[g * 8 + 2 * j] = fmaf(p.beta, f.x, v[g * 8 + 2 * j]);
-                  v[g * 8 + 2 * j + 1] = fmaf(p.beta, f.y, v[g * 8 + 2 * j + 1]);
-                }
-              }
-            }
-          }
-          if (p.act == 1) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
-          }
-          __half *dp = p.D + static_cast<long long>(row) * p.ldd + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g * 8 < ncols) {
-              uint4 out;
-              __half2 *o2 = reinterpret_cast<__half2 *>(&out);
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                o2[j] = __floats2half2_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
-              *reinterpret_cast<uint4 *>(dp + g * 8) = out;
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      epilogue_warp_block<BN>(p.ep, &tmD, t_row, m0 + quarter * 32, n0, stage_smem, lane, [&]() {
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      });
+    }
+    // Stores still in flight read this warp's staging tile: let them finish reading it.
+    if (lane == 0) bulk_wait_group_read_0();
+    __syncwarp();
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {
+      p.prof[5] = clock64() - t_begin;
+      p.prof[6] = t_wait;
     }
   }
 
@@ -294,7 +302,7 @@ EncodeFn get_encode_fn() {
 struct MapKey {
   const void *ptr;
   uint64_t inner, outer;
-  uint32_t box_inner, box_outer;
+  uint32_t box_inner, box_outer;  // box_outer | groups << 16 for the grouped 3-D form
   bool operator==(const MapKey &o) const {
     return ptr == o.ptr && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
            box_outer == o.box_outer;
@@ -314,6 +322,33 @@ std::mutex g_map_mutex;
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
 
 }  // namespace
+
+// Diagnostics (HOM_GEMM_PROFILE=1): a small device buffer the kernels fill with per-role
+// cycle counters of CTA 0, printed after a stream synchronisation.  Never on by default.
+static long long *g_profile_buf = nullptr;
+
+long long *profile_buffer() {
+  static bool checked = false;
+  if (!checked) {
+    checked = true;
+    if (std::getenv("HOM_GEMM_PROFILE")) {
+      if (cudaMalloc(&g_profile_buf, 16 * sizeof(long long)) != cudaSuccess) g_profile_buf = nullptr;
+    }
+  }
+  if (g_profile_buf) cudaMemset(g_profile_buf, 0, 16 * sizeof(long long));
+  return g_profile_buf;
+}
+
+void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream) {
+  long long h[16];
+  cudaStreamSynchronize(stream);
+  cudaMemcpy(h, g_profile_buf, sizeof(h), cudaMemcpyDeviceToHost);
+  fprintf(stderr,
+          "[hom] %s tiles %d grid %d kblocks %d | producer total %lld wait-empty %lld | mma total %lld "
+          "wait-full %lld wait-acc %lld | epilogue total %lld wait-full %lld | odd-CTA producer total "
+          "%lld wait-empty %lld\n",
+          what, tiles, grid, num_kb, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9]);
+}
 
 // 2-D fp16 tensor [outer, inner] (inner contiguous), 128-byte swizzle, zero fill.
 bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
@@ -352,6 +387,46 @@ bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_
   return true;
 }
 
+// Row-major fp16 matrix [rows, cols] with cols % 64 == 0, seen as a 3-D tensor
+// (64 columns, rows, cols / 64 column groups): one box of (64, box_rows, groups) lands in
+// shared memory as `groups` consecutive 128-byte-swizzled [box_rows x 64] sub-tiles, so one
+// TMA instruction fetches what would otherwise take one 2-D load per 64-column group.
+bool make_tensor_map_grouped(const void *ptr, uint64_t cols, uint64_t rows, uint32_t box_rows,
+                             uint32_t groups, CUtensorMap *out) {
+  MapKey key{ptr, cols, rows, 64u | 0x80000000u, box_rows | (groups << 16)};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeFn encode = get_encode_fn();
+  if (!encode) {
+    set_error(HOM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint64_t dims[3] = {64, rows, cols / 64};
+  cuuint64_t strides[2] = {cols * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, groups};
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims,
+                      strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(HOM_ERR_CUDA, "cuTensorMapEncodeTiled (grouped) failed (%d) for [%llu x %llu]",
+              static_cast<int>(r), static_cast<unsigned long long>(rows),
+              static_cast<unsigned long long>(cols));
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() > 8192) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return true;
+}
+
 namespace {
 
 template <int BN, bool B_NK>
@@ -368,105 +443,136 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
       return false;
     attr_set[dev] = true;
   }
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmD;
   if (!make_tensor_map_2d(pb.A, pb.K, pb.M, BK, BM, &tmA)) return false;
+  if (!make_tensor_map_2d(pb.D, pb.N, pb.M, 64, 32, &tmD)) return false;
+  const bool grouped = !B_NK && pb.N % 64 == 0;
   if (B_NK) {
     if (!make_tensor_map_2d(pb.B, pb.K, pb.N, BK, BN, &tmB)) return false;
+  } else if (grouped) {
+    if (!make_tensor_map_grouped(pb.B, pb.N, pb.K, BK, BN / 64, &tmB)) return false;
   } else {
     if (!make_tensor_map_2d(pb.B, pb.N, pb.K, 64, BK, &tmB)) return false;
   }
   Params p;
-  p.M = static_cast<int>(pb.M);
-  p.N = static_cast<int>(pb.N);
+  p.b_grouped = grouped ? 1 : 0;
+  p.ep.M = static_cast<int>(pb.M);
+  p.ep.N = static_cast<int>(pb.N);
   p.K = static_cast<int>(pb.K);
-  p.C = pb.C;
-  p.ldc = pb.N;
-  p.c_mode = pb.c_mode;
-  p.D = pb.D;
-  p.ldd = pb.N;
-  p.alpha = pb.alpha;
-  p.beta = pb.beta;
-  p.act = pb.act;
+  p.ep.C = pb.C;
+  p.ep.ldc = pb.N;
+  p.ep.c_mode = pb.c_mode;
+  p.ep.D = pb.D;
+  p.ep.ldd = pb.N;
+  p.ep.alpha = pb.alpha;
+  p.ep.beta = pb.beta;
+  p.ep.act = pb.act;
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
   p.num_tiles = m_blocks * p.n_blocks;
   p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
+  p.stages = Cfg::kStages;
+  if (const char *env = std::getenv("HOM_GEMM_STAGES")) {  // experiment knob
+    const int v = std::atoi(env);
+    if (v >= 1 && v < Cfg::kStages) p.stages = v;
+  }
   p.status = device_status_word();
+  p.prof = profile_buffer();
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   const double flops = 2.0 * pb.M * pb.N * pb.K;
   const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
                               static_cast<double>(pb.M) * pb.N) +
                        (pb.c_mode == 1 ? 2.0 * pb.M * pb.N : pb.c_mode == 2 ? 2.0 * pb.N : 0.0);
   LaunchScope scope(kOpGemm, flops, bytes);
-  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  if (!check_cuda(launch_pdl(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, 1, tmA, tmB,
+                             tmD, p),
+                  "gemm kernel launch"))
+    return false;
+  if (p.prof) profile_report("gemm 1-CTA", p.num_tiles, grid, p.num_kb, stream);
   return check_cuda(cudaGetLastError(), "gemm kernel launch");
 }
 
 struct ShapeRow {
   int64_t m, n, k;
   int act;
-  int bn;
+  int row;
 };
 
-// Per-shape choices for the BERT-base / BERT-large encoder GEMMs (M = batch*seq rows),
-// replacing the reference's autotune cache keyed on (M, N, K, activation).
+// Tile-table rows: 1-4 = one CTA per 128 x {64,128,192,256} tile; 5, 6 = one CTA pair per
+// 256 x {128,256} tile.
+struct TileRow {
+  int tile_m, tile_n, stages;
+  bool pair;
+};
+const TileRow kTileRows[7] = {
+    {0, 0, 0, false},      {128, 64, 8, false},  {128, 128, 6, false}, {128, 192, 5, false},
+    {128, 256, 4, false},  {256, 128, 8, true},  {256, 256, 6, true},
+};
+constexpr int kNumTileRows = 6;
+
+// Per-shape choices for the BERT-base encoder GEMMs (M = batch*seq rows), replacing the
+// reference's autotune cache keyed on (M, N, K, activation).
 const ShapeRow kShapeTable[] = {
-    {4096, 2304, 768, 0, 256},   // base QKV
-    {4096, 768, 768, 0, 192},    // base attention output projection (+ residual)
-    {4096, 3072, 768, 1, 256},   // base FFN1 + GELU
-    {4096, 768, 3072, 0, 192},   // base FFN2 (+ residual)
-    {512, 3072, 768, 1, 128},    // single fused GEMM + bias + GELU case
+    {4096, 2304, 768, 0, 6},   // base QKV
+    {4096, 768, 768, 0, 3},    // base attention output projection (+ residual)
+    {4096, 3072, 768, 1, 6},   // base FFN1 + GELU
+    {4096, 768, 3072, 0, 3},   // base FFN2 (+ residual)
+    {512, 3072, 768, 1, 2},    // single fused GEMM + bias + GELU case
 };
-
-int row_of_bn(int bn) { return bn == 64 ? 1 : bn == 128 ? 2 : bn == 192 ? 3 : 4; }
-int bn_of_row(int row) { return row == 1 ? 64 : row == 2 ? 128 : row == 3 ? 192 : row == 4 ? 256 : 0; }
 
 }  // namespace
 
-int select_bn(int64_t m, int64_t n, int64_t k, int act) {
+int select_tile_row(int64_t m, int64_t n, int64_t k, int act) {
+  if (const char *env = std::getenv("HOM_GEMM_TILE")) {  // experiment knob
+    const int v = std::atoi(env);
+    if (v >= 1 && v <= kNumTileRows) return v;
+  }
   for (const ShapeRow &r : kShapeTable)
-    if (r.m == m && r.n == n && r.k == k && r.act == act) return r.bn;
-  // Fewest waves of 148 CTAs weighted by per-tile cost (MMA columns + fixed overhead),
-  // counting the columns a ragged last tile wastes.
+    if (r.m == m && r.n == n && r.k == k && r.act == act) return r.row;
+  // Estimated time = waves x per-tile time.  A wave is 148 single-CTA tiles or 74 pair
+  // tiles; the per-tile time grows with the tile's N (MMA columns per K step) plus a fixed
+  // part, and a single CTA sustains a lower MMA rate than a pair (its TMA ring is shallower
+  // relative to the bytes it has to pull per K step).
   const int sms = sm_count();
-  const int64_t m_blocks = (m + BM - 1) / BM;
-  int best = 64;
+  int best = 1;
   double best_cost = 1e300;
-  const int cands[4] = {256, 192, 128, 64};
-  for (int bn : cands) {
-    const int64_t n_blocks = (n + bn - 1) / bn;
-    const int64_t tiles = m_blocks * n_blocks;
-    const int64_t waves = (tiles + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * (bn + 32);
+  for (int row = 1; row <= kNumTileRows; ++row) {
+    const TileRow &t = kTileRows[row];
+    const int64_t tiles = ((m + t.tile_m - 1) / t.tile_m) * ((n + t.tile_n - 1) / t.tile_n);
+    const int64_t slots = t.pair ? sms / 2 : sms;
+    const int64_t waves = (tiles + slots - 1) / slots;
+    const double per_tile = t.pair ? t.tile_n + 48.0 : 1.5 * t.tile_n + 48.0;
+    const double cost = static_cast<double>(waves) * per_tile;
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
-      best = bn;
+      best = row;
     }
   }
   return best;
 }
 
 int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, int *split_k) {
-  const int b = select_bn(m, n, k, act);
-  if (bn) *bn = b;
-  if (stages) *stages = b == 256 ? 4 : b == 192 ? 5 : b == 128 ? 6 : 8;
+  const int row = select_tile_row(m, n, k, act);
+  if (bn) *bn = kTileRows[row].tile_n;
+  if (stages) *stages = kTileRows[row].stages;
   if (split_k) *split_k = 1;
-  return row_of_bn(b);
+  return row;
 }
 
 bool run(const Problem &pb, int tile_row, cudaStream_t stream) {
   if (pb.M == 0 || pb.N == 0) return true;
-  int bn = bn_of_row(tile_row);
-  if (bn == 0) bn = select_bn(pb.M, pb.N, pb.K, pb.act);
+  if (tile_row < 1 || tile_row > kNumTileRows) tile_row = select_tile_row(pb.M, pb.N, pb.K, pb.act);
+  const TileRow &t = kTileRows[tile_row];
+  if (t.pair) return run_pair(pb, t.tile_n, stream);
   if (pb.b_is_nk) {
-    switch (bn) {
+    switch (t.tile_n) {
       case 64: return launch_variant<64, true>(pb, stream);
       case 128: return launch_variant<128, true>(pb, stream);
       case 192: return launch_variant<192, true>(pb, stream);
       default: return launch_variant<256, true>(pb, stream);
     }
   }
-  switch (bn) {
+  switch (t.tile_n) {
     case 64: return launch_variant<64, false>(pb, stream);
     case 128: return launch_variant<128, false>(pb, stream);
     case 192: return launch_variant<192, false>(pb, stream);

@@ -20,16 +20,28 @@ struct Problem {
   int act = 0;  // 1 = erf GELU
 };
 
-// Enqueues the GEMM; tile_row 1..4 forces the 128 x {64,128,192,256} tile, anything else
-// lets the tile table / heuristic decide.  Returns false (error recorded) on failure.
+// Enqueues the GEMM; tile_row 1..4 forces one CTA per 128 x {64,128,192,256} tile, 5..6 one
+// CTA pair per 256 x {128,256} tile; anything else lets the tile table / heuristic decide.
+// Returns false (error recorded) on failure.
 bool run(const Problem &pb, int tile_row, cudaStream_t stream);
+// The CTA-pair kernels (gemm_pair_sm100.cu); bn2 is 128 or 256.
+bool run_pair(const Problem &pb, int bn2, cudaStream_t stream);
 
-int select_bn(int64_t m, int64_t n, int64_t k, int act);
+int select_tile_row(int64_t m, int64_t n, int64_t k, int act);
 int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, int *split_k);
+
+// Diagnostics, enabled by HOM_GEMM_PROFILE=1 only: per-role cycle counters of CTA 0.
+long long *profile_buffer();
+void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream);
 
 // Cached cuTensorMapEncodeTiled for a 2-D fp16 tensor [outer, inner], 128-byte swizzle.
 bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
                         uint32_t box_outer, CUtensorMap *out);
+
+// Row-major [rows, cols] fp16 matrix, cols % 64 == 0, as (64, rows, cols/64): one box of
+// (64, box_rows, groups) becomes `groups` consecutive swizzled [box_rows x 64] sub-tiles.
+bool make_tensor_map_grouped(const void *ptr, uint64_t cols, uint64_t rows, uint32_t box_rows,
+                             uint32_t groups, CUtensorMap *out);
 
 }  // namespace gemm
 }  // namespace hom

@@ -73,9 +73,40 @@ enum OpKind : int32_t {
 };
 
 cudaStream_t current_stream();
+// Programmatic dependent launch is on unless HOM_DISABLE_PDL is set (diagnostics).
+bool pdl_enabled();
 // Host-mapped status word that device code writes on a bounded-wait expiry (device pointer).
 int *device_status_word();
 int sm_count();
+
+// Launches `kernel` with programmatic stream serialization allowed (and, when cluster_x > 1,
+// as clusters of that many CTAs along x).  Every kernel of this library calls
+// griddepcontrol.wait before its first dependent global-memory access, which is what makes the
+// relaxed launch order safe.
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, unsigned cluster_x, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[n].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  ++n;
+  if (cluster_x > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = cluster_x;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
+}
 
 // RAII bracket around one kernel launch: counts it and, when timing is enabled,
 // records events on the current stream.

@@ -386,7 +386,9 @@ void cutlassGemmF32(int64_t, void *, bool, int64_t, void *, bool, int64_t, void 
 
 void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *dstB, bool transb,
                  int64_t rankC, void *dstC, int64_t rankD, void *dstD, int64_t activation,
-                 float alpha, float beta, int32_t, int32_t) {
+                 float alpha, float beta, int32_t gemmNum, int32_t) {
+  // The reference ignores the two trailing integers on this path; here the first one is
+  // honoured as a tile-table row like cutlassGemmF16's gemmNum (0 = automatic).
   if (transa || !transb) {
     set_error(HOM_ERR_UNSUPPORTED, "nvteGemmF16: only transa=false, transb=true (B as [1,N,K])");
     return;
@@ -396,7 +398,7 @@ void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *ds
     return;
   }
   gemm_entry("nvteGemmF16", true, rankA, dstA, rankB, dstB, rankC, dstC, rankD, dstD, activation,
-             alpha, beta, 0);
+             alpha, beta, gemmNum);
 }
 
 void cutlassGemmWithVarMeanF16(int64_t, void *, int64_t, void *, int64_t, void *, int64_t, void *,

@@ -44,8 +44,9 @@ extern "C" {
 /* D = epilogue(alpha * A.B + beta * C); A [Bs,M,K], B [1,K,N], C/D [Bs,M,N], fp16 in and
  * out, fp32 accumulate and epilogue.  `activation` 1 = erf GELU, 0 = identity.  D may alias C.
  * C may also be [1,1,N] (bias broadcast over rows, as the reference's CPU matmulAddF32 does,
- * lib/ExecutionEngine/HandsOnRunnerUtils.cpp:258-266).  `gemmNum` > 0 selects a row of the
- * sm_100a tile table (0 or an unknown number = automatic); `splitKFactor` is a hint.
+ * lib/ExecutionEngine/HandsOnRunnerUtils.cpp:258-266).  `gemmNum` 1..6 selects a row of the
+ * sm_100a tile table (1-4: one CTA per 128 x {64,128,192,256} tile; 5-6: one CTA pair per
+ * 256 x {128,256} tile; 0 or any other number = automatic); `splitKFactor` is a hint.
  * Replaces lib/ExecutionEngine/HandsOnNVGPURunnerUtils.cu:104-116 and
  * include/NVGPUKernels/GemmRunner.h:244-310. */
 HOM_EXPORT void cutlassGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *dstB,
@@ -59,12 +60,13 @@ HOM_EXPORT void cutlassGemmF32(int64_t rankA, void *dstA, bool transa, int64_t r
                                int64_t activation, float alpha, float beta);
 
 /* D = act(A.B^T) (+ D when beta == 1 and C aliases D); A [Bs,M,K], B [1,N,K] with
- * transb == true, transa == false, alpha == 1, beta in {0,1}.
+ * transb == true, transa == false, alpha == 1, beta in {0,1}.  The reference ignores the two
+ * trailing integers; here the first is a tile-table row hint like cutlassGemmF16's gemmNum.
  * Replaces HandsOnNVGPURunnerUtils.cu:172-183 and GemmRunner.h:322-426. */
 HOM_EXPORT void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *dstB,
                             bool transb, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
-                            int64_t activation, float alpha, float beta, int32_t unused0,
-                            int32_t unused1);
+                            int64_t activation, float alpha, float beta, int32_t gemmNum,
+                            int32_t unused);
 
 /* GEMM whose epilogue also emits per-row partial statistics, and the GEMM that consumes
  * them (HandsOnNVGPURunnerUtils.cu:118-170, :191-222).  Not emitted by the compiler for
@@ -201,7 +203,7 @@ typedef struct HomOpTiming {
 HOM_EXPORT void homOpTimingEnable(int enable);
 HOM_EXPORT int64_t homOpTimingCollect(HomOpTiming *out, int64_t capacity);
 
-/* The tile the GEMM family would run for (M, N, K, activation): BN (tile is 128 x BN x 64),
+/* The tile the GEMM family would run for (M, N, K, activation): the tile's N extent,
  * pipeline stages and split-K.  Returns the tile-table row number (usable as gemmNum). */
 HOM_EXPORT int32_t homGemmQueryTile(int64_t m, int64_t n, int64_t k, int64_t activation,
                                     int32_t *bn, int32_t *stages, int32_t *splitK);

@@ -29,16 +29,16 @@ def _run_gemm(hom, dev, A, B, C, *, nk=False, act=0, alpha=1.0, beta=0.0, tile=0
         tD = torch.full(A.shape[:-1] + (n,), float("nan"), dtype=torch.float16, device=dev)
         tC = to_dev(C, dev) if C is not None else tD
     if nk:
-        hom.nvteGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta)
+        hom.nvteGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta, gemmNum=tile)
     else:
         hom.cutlassGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta, gemmNum=tile)
     hom.synchronize()
     return tD.cpu().numpy()
 
 
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6])
 @pytest.mark.parametrize("shape", [(1, 128, 64, 64), (2, 128, 256, 128), (1, 200, 136, 72),
-                                   (3, 100, 520, 200), (1, 384, 768, 1024)])
+                                   (3, 100, 520, 200), (1, 384, 768, 1024), (5, 128, 640, 320)])
 def test_gemm_plain_all_tiles(hom, cuda, oracle, shape, tile):
     bs, m, n, k = shape
     rng = _rng(1)
@@ -59,7 +59,7 @@ def test_gemm_bias_gelu_config1(hom, cuda, oracle, seed):
     assert_close_f16(got, oracle.gemm_f16(A, B, bias, beta=1.0, act=1), "config 1")
 
 
-@pytest.mark.parametrize("tile", [0, 2, 3, 4])
+@pytest.mark.parametrize("tile", [0, 2, 3, 4, 5, 6])
 def test_gemm_residual_aliases_output(hom, cuda, oracle, tile):
     rng = _rng(7)
     A = rng.normal(0, 1, (2, 128, 256)).astype(np.float16)
@@ -78,15 +78,16 @@ def test_gemm_alpha_beta_gelu(hom, cuda, oracle):
     assert_close_f16(got, oracle.gemm_f16(A, B, C, alpha=0.5, beta=-1.5, act=1), "alpha/beta")
 
 
+@pytest.mark.parametrize("tile", [0, 4, 5, 6])
 @pytest.mark.parametrize("shape", [(2, 128, 256, 128), (1, 300, 1024, 264), (4, 128, 768, 3072)])
 @pytest.mark.parametrize("act,beta", [(0, 0.0), (1, 0.0), (0, 1.0)])
-def test_nvte_gemm_transb(hom, cuda, oracle, shape, act, beta):
+def test_nvte_gemm_transb(hom, cuda, oracle, shape, act, beta, tile):
     bs, m, n, k = shape
     rng = _rng(11)
     A = rng.uniform(-1, 1, (bs, m, k)).astype(np.float16)
     B = rng.normal(0, 0.03, (1, n, k)).astype(np.float16)
     C = rng.normal(0, 1, (bs, m, n)).astype(np.float16) if beta else None
-    got = _run_gemm(hom, cuda, A, B, C, nk=True, act=act, beta=beta, alias=bool(beta))
+    got = _run_gemm(hom, cuda, A, B, C, nk=True, act=act, beta=beta, alias=bool(beta), tile=tile)
     assert_close_f16(got, oracle.gemm_f16(A, B, C, b_is_nk=True, act=act, beta=beta),
                      f"nvte {shape} act {act} beta {beta}")
 
@@ -100,15 +101,16 @@ def test_gemm_constant_inputs_like_reference_harness(hom, cuda):
     assert np.abs(got - 768 * 0.02).max() <= 1e-1
 
 
+@pytest.mark.parametrize("tile", [0, 6])
 @pytest.mark.parametrize("m,n,k,act,res", [(4096, 2304, 768, 0, False), (4096, 768, 768, 0, True),
                                            (4096, 3072, 768, 1, False), (4096, 768, 3072, 0, True)])
-def test_gemm_bert_base_shapes_sampled_rows(hom, cuda, oracle, m, n, k, act, res):
+def test_gemm_bert_base_shapes_sampled_rows(hom, cuda, oracle, m, n, k, act, res, tile):
     """BERT-base b32 x s128 GEMMs at full size; the oracle checks 3 rows of every 128-row block."""
     rng = _rng(21)
     A = rng.normal(0, 1, (32, 128, k)).astype(np.float16)
     B = rng.normal(0, 0.02, (1, k, n)).astype(np.float16)
     C = rng.normal(0, 1, (32, 128, n)).astype(np.float16) if res else None
-    got = _run_gemm(hom, cuda, A, B, C, act=act, beta=1.0 if res else 0.0, alias=res)
+    got = _run_gemm(hom, cuda, A, B, C, act=act, beta=1.0 if res else 0.0, alias=res, tile=tile)
     rows = np.concatenate([np.arange(0, m, 128), np.arange(77, m, 128), np.arange(127, m, 128)])
     A2, got2 = A.reshape(m, k)[rows], got.reshape(m, n)[rows]
     C2 = C.reshape(m, n)[rows] if res else None
