@@ -478,6 +478,17 @@ def run_gpu_arm(args, cfg, workload):
         d["ms"] += ms
         d["flops"] += flops
         d["bytes"] += nbytes
+    # GEMM launches grouped by their algorithmic FLOPs (= by shape)
+    gemm_shapes = {}
+    for kind, ms, flops, nbytes in records:
+        if kind == 1:
+            d = gemm_shapes.setdefault(f"{flops / 1e9:.2f}_gflop", {"launches": 0, "ms": 0.0, "flops": flops})
+            d["launches"] += 1
+            d["ms"] += ms
+    gemm_by_shape = {k: {"launches_per_step": v["launches"] // n_prof,
+                         "avg_us": 1e3 * v["ms"] / v["launches"],
+                         "tflops": v["flops"] * v["launches"] / (v["ms"] / 1e3) / 1e12}
+                     for k, v in gemm_shapes.items()}
     peaks, peak_src = load_peaks()
     gemm = per_kind.get("gemm", {"launches": 1, "ms": float("nan"), "flops": 0.0})
     gemm_tflops = gemm["flops"] / (gemm["ms"] / 1e3) / 1e12 if gemm["ms"] > 0 else float("nan")
@@ -542,6 +553,7 @@ def run_gpu_arm(args, cfg, workload):
             "gpu_launches": args.steps * prog.launches_per_forward(),
             "roofline": roofline,
             "kernels": kernel_share,
+            "gemm_by_shape": gemm_by_shape,
             "clocks": clocks.summary(),
             "output_gather_ms": gather_ms,
         }

@@ -89,27 +89,43 @@ __device__ __forceinline__ void epilogue_store_32(const EpilogueParams &ep, cons
   }
 }
 
-// Bytes of shared-memory staging each epilogue warp owns: 32 rows x 64 fp16 columns.
-constexpr uint32_t kEpilogueStageBytes = 32 * 128;
+// Epilogue warps per CTA and the shared-memory staging each of them owns: two
+// [32 rows x 64 fp16 columns] tiles, used alternately so that a TMA store can still be reading
+// one while the warp fills the other.
+constexpr int kEpilogueWarps = 8;
+constexpr uint32_t kEpilogueTileBytes = 32 * 128;
+constexpr uint32_t kEpilogueStageBytes = 2 * kEpilogueTileBytes;
+constexpr uint32_t kEpilogueStagingBytes = kEpilogueWarps * kEpilogueStageBytes;
 
-// One warp drains a [32 rows x NCOLS] block of an accumulator: thread `lane` owns output row
-// `row0 + lane`.  Per 64-column step the warp reads the accumulator (two tcgen05.ld issued
-// back to back), applies the epilogue in fp32, writes the fp16 results into its 128-byte-
-// swizzled staging tile and lets one lane hand the tile to TMA, which writes full 128-byte
-// rows to global memory and clips rows >= M and columns >= N.  `tmem_addr` already selects
-// the warp's lane quarter and the block's first column.  After the last accumulator read the
-// function calls `release()` (the accumulator may be overwritten) while the stores drain.
-template <int NCOLS, typename Release>
+// One warp drains a [32 rows x ncols] block of an accumulator (ncols a multiple of 64, possibly
+// 0): thread `lane` owns output row `row0 + lane`.  Per 64-column step the warp reads the
+// accumulator (two tcgen05.ld issued back to back), applies the epilogue in fp32, writes the
+// fp16 results into one of its two 128-byte-swizzled staging tiles and lets one lane hand
+// the tile to TMA, which writes full 128-byte rows to global memory and clips rows >= M and
+// columns >= N.  `tmem_addr` already selects the warp's lane quarter and the block's first
+// column; `n_stores` counts this warp's stores so far (selects the staging tile).  After the
+// last accumulator read the function calls `release()` (the accumulator may be overwritten)
+// while the stores drain.
+template <typename Release>
 __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
-                                                    uint32_t tmem_addr, int row0, int col0,
-                                                    uint32_t stage_smem, int lane, Release release) {
+                                                    uint32_t tmem_addr, int row0, int col0, int ncols,
+                                                    uint32_t stage_smem, int lane, uint32_t &n_stores,
+                                                    Release release) {
   using namespace hom::ptx;
   const int row = row0 + lane;
   const bool row_ok = row < ep.M;
-  const uint32_t my_row = stage_smem + lane * 128;
+  const int steps = ncols / 64;
+  if (steps == 0) {
+    tc_fence_before_sync();
+    __syncwarp();
+    release();
+    return;
+  }
 #pragma unroll 1
-  for (int step = 0; step < NCOLS / 64; ++step) {
+  for (int step = 0; step < steps; ++step) {
     const int c0 = col0 + step * 64;
+    const uint32_t tile = stage_smem + (n_stores & 1u) * kEpilogueTileBytes;
+    const uint32_t my_row = tile + lane * 128;
     uint32_t acc[2][32];
     tmem_ld_32x32(tmem_addr + step * 64, acc[0]);
     tmem_ld_32x32(tmem_addr + step * 64 + 32, acc[1]);
@@ -124,13 +140,13 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
       }
     }
     tmem_ld_wait();
-    if (step == NCOLS / 64 - 1) {
+    if (step == steps - 1) {
       tc_fence_before_sync();
       __syncwarp();
       release();
     }
-    // The staging tile may be rewritten once the previous store has read it.
-    if (lane == 0) bulk_wait_group_read_0();
+    // This staging tile was last handed to TMA two stores ago: that read must be over.
+    if (lane == 0) bulk_wait_group_read_1();
     __syncwarp();
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
@@ -163,10 +179,11 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
     }
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0 && c0 < ep.N && row0 < ep.M) {
-      tma_store_2d(tmD, stage_smem, c0, row0);
-      bulk_commit_group();
+    if (lane == 0) {
+      if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, tile, c0, row0);
+      bulk_commit_group();  // one group per step (possibly empty) keeps the tile rotation exact
     }
+    ++n_stores;
   }
 }
 

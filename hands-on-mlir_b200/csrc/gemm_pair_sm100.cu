@@ -5,7 +5,7 @@
 // step, and each CTA drains its 128 accumulator rows from its own tensor memory.  Compared
 // with one CTA per 128 x 256 tile this halves the B bytes every SM pulls through L2 and
 // shared memory for the same MMA time, which is what the TMA ring needs to keep the tensor
-// pipe fed; the freed shared memory holds six stages instead of four.
+// pipe fed; the freed shared memory holds five stages and the epilogue staging.
 //
 //   warp 0      TMA producer (one thread)
 //   warp 1      tensor-memory allocation (both CTAs) and MMA issue (even CTA only)
@@ -31,7 +31,6 @@ namespace {
 
 constexpr int BK = 64;
 constexpr int kPairThreads = 320;
-constexpr int kEpilogueWarps = 8;
 constexpr uint32_t kABytes = 128 * BK * 2;
 
 template <int BN2>
@@ -39,9 +38,9 @@ struct PairCfg {
   static constexpr int kHalfN = BN2 / 2;
   static constexpr uint32_t kBBytes = kHalfN * BK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN2 == 256 ? 6 : 8;
+  static constexpr int kStages = BN2 == 256 ? 5 : 6;
   static constexpr uint32_t kTmemCols = 2 * BN2;  // two accumulators; 512 or 256
-  static constexpr uint32_t kStagingBytes = kEpilogueWarps * kEpilogueStageBytes;
+  static constexpr uint32_t kStagingBytes = kEpilogueStagingBytes;
   static constexpr uint32_t kBarrierBytes = 8 * (2 * kStages + 4) + 16;
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
@@ -241,6 +240,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int col_half = (warp - 2) >> 2;  // which half of the tile's columns
     const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
     int it = 0;
+    uint32_t n_stores = 0;
     long long t_wait = 0, t_begin = clock64();
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++it) {
@@ -256,7 +256,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int n0 = (tile % p.n_blocks) * BN2 + col_half * HALF;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_half * HALF;
-      epilogue_warp_block<HALF>(p.ep, &tmD, t_row, m0 + quarter * 32, n0, stage_smem, lane, [&]() {
+      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, HALF, stage_smem, lane, n_stores, [&]() {
         if (lane == 0) {
           if (rank == 0) mbar_arrive(tempty_bar(acc));
           else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));

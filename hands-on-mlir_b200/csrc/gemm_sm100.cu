@@ -6,8 +6,9 @@
 //             128-byte-swizzled shared-memory stages (mbarrier full/empty hand-off);
 //   warp 1    one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
 //             accumulators and releases stages / publishes accumulators with tcgen05.commit;
-//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (one output row per thread,
-//             64 columns at a time), fp32 alpha/beta/bias/erf-GELU, one fp16 rounding, results
+//   warps 2-9 epilogue (two warps per tensor-memory lane quarter, each a share of the tile's
+//             columns): tcgen05.ld the finished accumulator (one output row per thread, 64
+//             columns at a time), fp32 alpha/beta/bias/erf-GELU, one fp16 rounding, results
 //             staged in swizzled shared memory and written out by TMA stores, while warp 1
 //             already fills the other accumulator.
 //
@@ -32,17 +33,20 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kABytes = BM * BK * 2;
 
 template <int BN>
 struct TileCfg {
   static constexpr uint32_t kBBytes = BN * BK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  // As many stages as fit in ~196 KB.
-  static constexpr int kStages = BN == 256 ? 4 : BN == 192 ? 5 : BN == 128 ? 6 : 8;
+  // As many stages as fit beside the 64 KB of epilogue staging.
+  static constexpr int kStages = BN == 256 ? 3 : BN == 192 ? 4 : BN == 128 ? 5 : 6;
+  // Columns drained by the first / second group of four epilogue warps (multiples of 64).
+  static constexpr int kCols0 = BN == 64 ? 64 : BN == 192 ? 128 : BN / 2;
+  static constexpr int kCols1 = BN - kCols0;
   static constexpr uint32_t kTmemCols = BN == 64 ? 128 : BN == 128 ? 256 : 512;
-  static constexpr uint32_t kStagingBytes = 4 * kEpilogueStageBytes;  // one tile per epilogue warp
+  static constexpr uint32_t kStagingBytes = kEpilogueStagingBytes;
   static constexpr uint32_t kBarrierBytes = 8 * (2 * kStages + 4) + 16;
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
@@ -91,6 +95,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  const long long t_entry = p.prof ? clock64() : 0;
+  unsigned long long g_entry = 0;
+  if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -99,7 +106,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), kEpilogueWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -112,6 +119,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[10] = clock64() - t_entry;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -242,7 +250,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else {
     // --------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int group = (warp - 2) >> 2;  // first or second group of columns
+    const int col_begin = group == 0 ? 0 : Cfg::kCols0;
+    const int ncols = group == 0 ? Cfg::kCols0 : Cfg::kCols1;
     const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
+    uint32_t n_stores = 0;
     int it = 0;
     long long t_wait = 0, t_begin = clock64();
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
@@ -257,10 +269,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_after_sync();
       const int m0 = (tile / p.n_blocks) * BM;
       const int n0 = (tile % p.n_blocks) * BN;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      epilogue_warp_block<BN>(p.ep, &tmD, t_row, m0 + quarter * 32, n0, stage_smem, lane, [&]() {
-        if (lane == 0) mbar_arrive(tempty_bar(acc));
-      });
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + col_begin;
+      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, ncols, stage_smem, lane,
+                          n_stores, [&]() {
+                            if (lane == 0) mbar_arrive(tempty_bar(acc));
+                          });
     }
     // Stores still in flight read this warp's staging tile: let them finish reading it.
     if (lane == 0) bulk_wait_group_read_0();
@@ -276,6 +290,18 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 32) {
+    unsigned long long g_exit;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_exit));
+    p.prof[11] = clock64() - t_entry;
+    p.prof[12] = static_cast<long long>(g_entry);
+    p.prof[13] = static_cast<long long>(g_exit);
+    // ring of (entry, exit) wall-clock stamps of the last launches (timeline diagnostics)
+    const long long slot = p.prof[15] & 15;
+    p.prof[16 + 2 * slot] = static_cast<long long>(g_entry);
+    p.prof[17 + 2 * slot] = static_cast<long long>(g_exit);
+    p.prof[15] += 1;
   }
 }
 
@@ -332,22 +358,25 @@ long long *profile_buffer() {
   if (!checked) {
     checked = true;
     if (std::getenv("HOM_GEMM_PROFILE")) {
-      if (cudaMalloc(&g_profile_buf, 16 * sizeof(long long)) != cudaSuccess) g_profile_buf = nullptr;
+      if (cudaMalloc(&g_profile_buf, 64 * sizeof(long long)) != cudaSuccess) g_profile_buf = nullptr;
+      else cudaMemset(g_profile_buf, 0, 64 * sizeof(long long));
     }
   }
-  if (g_profile_buf) cudaMemset(g_profile_buf, 0, 16 * sizeof(long long));
+  if (g_profile_buf && !std::getenv("HOM_GEMM_TIMELINE")) cudaMemset(g_profile_buf, 0, 15 * sizeof(long long));
   return g_profile_buf;
 }
 
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream) {
+  if (std::getenv("HOM_GEMM_TIMELINE")) return;  // stamps are read back by the caller
   long long h[16];
   cudaStreamSynchronize(stream);
   cudaMemcpy(h, g_profile_buf, sizeof(h), cudaMemcpyDeviceToHost);
   fprintf(stderr,
           "[hom] %s tiles %d grid %d kblocks %d | producer total %lld wait-empty %lld | mma total %lld "
           "wait-full %lld wait-acc %lld | epilogue total %lld wait-full %lld | odd-CTA producer total "
-          "%lld wait-empty %lld\n",
-          what, tiles, grid, num_kb, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9]);
+          "%lld wait-empty %lld | setup %lld kernel %lld cycles, entry %lld ns, exit-entry %lld ns\n",
+          what, tiles, grid, num_kb, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9], h[10], h[11],
+          h[12], h[13] - h[12]);
 }
 
 // 2-D fp16 tensor [outer, inner] (inner contiguous), 128-byte swizzle, zero fill.
@@ -505,8 +534,8 @@ struct TileRow {
   bool pair;
 };
 const TileRow kTileRows[7] = {
-    {0, 0, 0, false},      {128, 64, 8, false},  {128, 128, 6, false}, {128, 192, 5, false},
-    {128, 256, 4, false},  {256, 128, 8, true},  {256, 256, 6, true},
+    {0, 0, 0, false},      {128, 64, 6, false},  {128, 128, 5, false}, {128, 192, 4, false},
+    {128, 256, 3, false},  {256, 128, 6, true},  {256, 256, 5, true},
 };
 constexpr int kNumTileRows = 6;
 

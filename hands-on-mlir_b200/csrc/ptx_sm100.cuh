@@ -170,6 +170,11 @@ __device__ __forceinline__ void bulk_wait_group_read_0() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
+// All but the most recent of this thread's bulk groups have finished reading shared memory.
+__device__ __forceinline__ void bulk_wait_group_read_1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+
 // All of this thread's bulk groups have completed (writes performed).
 __device__ __forceinline__ void bulk_wait_group_0() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

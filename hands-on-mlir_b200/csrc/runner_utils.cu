@@ -593,6 +593,13 @@ void printMemrefSizeF16(int64_t rank, void *d) { print_sizes(rank, d); }
 void printMemrefSizeI64(int64_t rank, void *d) { print_sizes(rank, d); }
 void printMemrefSizeI32(int64_t rank, void *d) { print_sizes(rank, d); }
 
+// Diagnostics only (HOM_GEMM_PROFILE=1 HOM_GEMM_TIMELINE=1): copies the 64-word profile buffer.
+__attribute__((visibility("default"))) void homDebugReadGemmProfile(long long *out) {
+  long long *buf = hom::gemm::profile_buffer();
+  cudaDeviceSynchronize();
+  if (buf) cudaMemcpy(out, buf, 64 * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+
 void homSetConstantDir(const char *dir) {
   std::lock_guard<std::mutex> lock(g_dir_mutex);
   g_constant_dir = dir ? dir : "";
