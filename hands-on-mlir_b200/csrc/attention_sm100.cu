@@ -11,6 +11,9 @@
 // Replaces the reference's cuDNN fused attention behind TransformerEngine
 // (include/NVGPUKernels/BertAttentionRunner.h:52-136: layout BS3HD, no bias, padding mask,
 // no dropout, inference).
+#include <mutex>
+#include <unordered_map>
+
 #include "attention_sm100.cuh"
 #include "gemm_sm100.cuh"
 #include "ptx_sm100.cuh"
@@ -278,6 +281,247 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Sequences of at most 128 tokens: one KV tile per (batch, head), so nothing is rescaled.
+// P overwrites the Q|K tiles once S has been computed from them, O reuses S's tensor-memory
+// columns, and the finished 128 x 64 output tile is staged over the V tile and written by one
+// TMA store through a 3-D [hidden, seq, batch] view of the output (rows beyond seq are
+// clipped).  48 KB of shared memory and 128 tensor-memory columns per CTA let four CTAs share
+// an SM, which is what hides the load -> MMA -> softmax -> MMA -> store latency chain.
+constexpr uint32_t kSmemBytes1 = 3 * kTileBytes + 64 + 1024;
+
+__global__ void __launch_bounds__(kThreads, 4)
+attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
+                                 const __grid_constant__ CUtensorMap tmOut, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int hidden = p.heads * kHeadDim;
+
+  const uint32_t smem_q = smem_base, smem_k = smem_base + kTileBytes, smem_v = smem_base + 2 * kTileBytes;
+  const uint32_t smem_p = smem_base;  // two 128 x 64 sub-tiles over Q|K
+  const uint32_t bar_load = smem_base + 3 * kTileBytes;
+  const uint32_t bar_s = bar_load + 8, bar_o = bar_load + 16;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + 3 * kTileBytes + 24);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  if (tid == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmQKV);
+    prefetch_tensormap(&tmOut);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 128);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+
+  pdl_wait();  // cu_seqlens and the packed QKV come from earlier kernels of the stream
+  int len = p.cu_seqlens[batch + 1] - p.cu_seqlens[batch];
+  len = max(0, min(len, p.seq));
+
+  bool ok = true;
+  float inv = 0.f;
+  if (len > 0) {
+    if (tid == 0) {
+      const int row_base = batch * p.seq;
+      mbar_arrive_expect_tx(bar_load, 3 * kTileBytes);
+      tma_load_2d(smem_q, &tmQKV, bar_load, head * kHeadDim, row_base);
+      tma_load_2d(smem_k, &tmQKV, bar_load, hidden + head * kHeadDim, row_base);
+      tma_load_2d(smem_v, &tmQKV, bar_load, 2 * hidden + head * kHeadDim, row_base);
+      if (mbar_wait(bar_load, 0, abort_flag, p.status, kDevWaitTimeoutAttention)) {
+        tc_fence_after_sync();
+        constexpr uint32_t idesc_s = make_idesc_f16(kTile, kTile, false, false);
+#pragma unroll
+        for (int k = 0; k < kHeadDim / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(smem_q + k * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_k + k * 32, 16, 1024);
+          tc_mma_f16_ss(tmem_acc, da, db, idesc_s, k != 0 ? 1u : 0u);
+        }
+        tc_commit(bar_s);
+      }
+    }
+    ok = mbar_wait(bar_s, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
+    ok = __syncthreads_and(ok);
+    if (ok) {
+      tc_fence_after_sync();
+      // softmax over the valid keys: one query row per thread
+      float m_row = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kTile / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < len) m_row = fmaxf(m_row, __uint_as_float(r[i]) * p.scale_log2);
+      }
+      float l_row = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kTile / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
+        tmem_ld_wait();
+        const uint32_t sub = smem_p + (c >> 1) * kTileBytes + tid * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i0 = g * 8 + 2 * j;
+            float e0 = exp2f(fmaf(__uint_as_float(r[i0]), p.scale_log2, -m_row));
+            float e1 = exp2f(fmaf(__uint_as_float(r[i0 + 1]), p.scale_log2, -m_row));
+            e0 = (c * 32 + i0 < len) ? e0 : 0.f;
+            e1 = (c * 32 + i0 + 1 < len) ? e1 : 0.f;
+            l_row += e0 + e1;
+            const __half2 h = __floats2half2_rn(e0, e1);
+            w[j] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+          const uint32_t chunk = (c & 1) * 4 + g;
+          const uint32_t addr = sub + ((chunk ^ (tid & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                       "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+      inv = (tid < len && l_row > 0.f) ? 1.f / l_row : 0.f;
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncthreads();  // P complete, and every thread is done reading S
+      if (tid == 0) {
+        tc_fence_after_sync();
+        constexpr uint32_t idesc_o = make_idesc_f16(kTile, kHeadDim, false, true);
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k) {
+          const uint64_t da =
+              make_smem_desc_sw128(smem_p + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_v + k * 2048, kTileBytes, 1024);
+          tc_mma_f16_ss(tmem_acc, da, db, idesc_o, k != 0 ? 1u : 0u);
+        }
+        tc_commit(bar_o);
+      }
+      ok = mbar_wait(bar_o, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
+      ok = __syncthreads_and(ok);
+    }
+  }
+
+  if (ok) {
+    if (len > 0) tc_fence_after_sync();
+    // O (or zeros for padded rows / empty sequences) -> swizzled staging over the V tile
+    const uint32_t my_row = smem_v + tid * 128;
+#pragma unroll
+    for (int c = 0; c < kHeadDim / 32; ++c) {
+      uint32_t r[32];
+      if (len > 0) {
+        tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
+        tmem_ld_wait();
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = len > 0 ? __uint_as_float(r[g * 8 + 2 * j]) * inv : 0.f;
+          const float b = len > 0 ? __uint_as_float(r[g * 8 + 2 * j + 1]) * inv : 0.f;
+          const __half2 h = (inv != 0.f) ? __floats2half2_rn(a, b) : __floats2half2_rn(0.f, 0.f);
+          w[j] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        const uint32_t chunk = c * 4 + g;
+        const uint32_t addr = my_row + ((chunk ^ (tid & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                     "r"(w[2]), "r"(w[3])
+                     : "memory");
+      }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile(
+          "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+          :
+          : "l"(reinterpret_cast<uint64_t>(&tmOut)), "r"(smem_v), "r"(head * kHeadDim), "r"(0),
+            "r"(batch)
+          : "memory");
+      bulk_commit_group();
+      bulk_wait_group_read_0();
+    }
+  } else if (tid == 0) {
+    // Let copies that are still in flight land before the shared memory is released.
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar_load, 0) && clock64() - t0 < 200000000LL) {
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_acc, 128);
+  }
+}
+
+}  // namespace
+
+namespace {
+
+// Output [bs, seq, hidden] fp16 as a 3-D tensor (hidden, seq, bs) with 64 x 128 x 1 boxes.
+bool make_out_map(const void *ptr, uint64_t hidden, uint64_t seq, uint64_t bs, CUtensorMap *out) {
+  static std::mutex mu;
+  static std::unordered_map<uint64_t, CUtensorMap> cache;
+  const uint64_t key = reinterpret_cast<uint64_t>(ptr) ^ (hidden << 48) ^ (seq << 32) ^ (bs << 20);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void *sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault,
+                                       &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess) {
+    set_error(HOM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint64_t dims[3] = {hidden, seq, bs};
+  cuuint64_t strides[2] = {hidden * 2, hidden * seq * 2};
+  cuuint32_t box[3] = {kHeadDim, kTile, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = reinterpret_cast<EncodeFn>(sym)(
+      out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, elem,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(HOM_ERR_CUDA, "cuTensorMapEncodeTiled (attention output) failed (%d)", static_cast<int>(r));
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
 }  // namespace
 
 bool run(const Problem &pb, cudaStream_t stream) {
@@ -296,6 +540,7 @@ bool run(const Problem &pb, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(pb.bs) * pb.seq;
   const uint64_t cols = 3ull * pb.heads * kHeadDim;
   if (!gemm::make_tensor_map_2d(pb.qkv, cols, rows, kHeadDim, kTile, &tm)) return false;
+  const bool single_tile = pb.seq <= kTile;
   Params p;
   p.cu_seqlens = pb.cu_seqlens;
   p.out = pb.out;
@@ -309,6 +554,21 @@ bool run(const Problem &pb, cudaStream_t stream) {
   const double flops = 4.0 * d * pb.heads * pb.bs * static_cast<double>(pb.seq) * pb.seq;
   const double bytes = 2.0 * rows * cols + 2.0 * rows * pb.heads * d + 4.0 * (pb.bs + 1);
   LaunchScope scope(kOpAttention, flops, bytes);
+  if (single_tile) {
+    static bool attr1_set[64] = {};
+    if (dev >= 0 && dev < 64 && !attr1_set[dev]) {
+      if (!check_cuda(cudaFuncSetAttribute(attention_f16_single_tile_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes1),
+                      "cudaFuncSetAttribute(attention)"))
+        return false;
+      attr1_set[dev] = true;
+    }
+    CUtensorMap tm_out;
+    if (!make_out_map(pb.out, pb.heads * kHeadDim, pb.seq, pb.bs, &tm_out)) return false;
+    return check_cuda(launch_pdl(attention_f16_single_tile_kernel, grid, dim3(kThreads), kSmemBytes1,
+                                 stream, 1, tm, tm_out, p),
+                      "attention kernel launch");
+  }
   return check_cuda(launch_pdl(attention_f16_kernel, grid, dim3(kThreads), kSmemBytes, stream, 1, tm, p),
                     "attention kernel launch");
 }

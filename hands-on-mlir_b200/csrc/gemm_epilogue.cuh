@@ -106,14 +106,29 @@ constexpr uint32_t kEpilogueStagingBytes = kEpilogueWarps * kEpilogueStageBytes;
 // column; `n_stores` counts this warp's stores so far (selects the staging tile).  After the
 // last accumulator read the function calls `release()` (the accumulator may be overwritten)
 // while the stores drain.
+// Requests the residual / bias values of one 64-column row segment (row `row`, columns
+// [c0, c0 + 64)); out-of-range groups come back as zeros.
+__device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int row, int c0, uint4 (&cval)[8]) {
+  if (ep.c_mode == 0) return;
+  const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
+  const bool row_ok = ep.c_mode == 2 || row < ep.M;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const bool ok = row_ok && c0 + g * 8 < ep.N;
+    cval[g] = ok ? *reinterpret_cast<const uint4 *>(cp + g * 8) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+// `cfirst` holds the residual / bias values of the block's first step, requested by the caller
+// (epilogue_load_c) before it waited for the accumulator so that their latency hides behind
+// the main loop; the values of each later step are requested one step ahead.
 template <typename Release>
 __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
                                                     uint32_t tmem_addr, int row0, int col0, int ncols,
                                                     uint32_t stage_smem, int lane, uint32_t &n_stores,
-                                                    Release release) {
+                                                    uint4 (&cfirst)[8], Release release) {
   using namespace hom::ptx;
   const int row = row0 + lane;
-  const bool row_ok = row < ep.M;
   const int steps = ncols / 64;
   if (steps == 0) {
     tc_fence_before_sync();
@@ -129,16 +144,10 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
     uint32_t acc[2][32];
     tmem_ld_32x32(tmem_addr + step * 64, acc[0]);
     tmem_ld_32x32(tmem_addr + step * 64 + 32, acc[1]);
-    // Residual / bias values for this row segment, requested before the accumulator wait.
     uint4 cval[8];
-    if (ep.c_mode != 0) {
-      const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const bool ok = (ep.c_mode == 2 || row_ok) && c0 + g * 8 < ep.N;
-        cval[g] = ok ? *reinterpret_cast<const uint4 *>(cp + g * 8) : make_uint4(0, 0, 0, 0);
-      }
-    }
+    for (int g = 0; g < 8; ++g) cval[g] = cfirst[g];
+    if (step + 1 < steps) epilogue_load_c(ep, row, c0 + 64, cfirst);  // next step's values
     tmem_ld_wait();
     if (step == steps - 1) {
       tc_fence_before_sync();

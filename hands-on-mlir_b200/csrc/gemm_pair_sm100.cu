@@ -246,17 +246,20 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
+      const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
+      const int n0 = (tile % p.n_blocks) * BN2 + col_half * HALF;
+      uint4 cfirst[8];
+      epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cfirst);
       const long long tw = p.prof ? clock64() : 0;
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (p.prof) t_wait += clock64() - tw;
       tc_fence_after_sync();
-      const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
-      const int n0 = (tile % p.n_blocks) * BN2 + col_half * HALF;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_half * HALF;
-      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, HALF, stage_smem, lane, n_stores, [&]() {
+      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, HALF, stage_smem, lane, n_stores,
+                          cfirst, [&]() {
         if (lane == 0) {
           if (rank == 0) mbar_arrive(tempty_bar(acc));
           else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));

@@ -261,18 +261,20 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
+      const int m0 = (tile / p.n_blocks) * BM;
+      const int n0 = (tile % p.n_blocks) * BN;
+      uint4 cfirst[8];
+      if (ncols > 0) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cfirst);
       const long long tw = p.prof ? clock64() : 0;
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (p.prof) t_wait += clock64() - tw;
       tc_fence_after_sync();
-      const int m0 = (tile / p.n_blocks) * BM;
-      const int n0 = (tile % p.n_blocks) * BN;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + col_begin;
       epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, ncols, stage_smem, lane,
-                          n_stores, [&]() {
+                          n_stores, cfirst, [&]() {
                             if (lane == 0) mbar_arrive(tempty_bar(acc));
                           });
     }
