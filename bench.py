@@ -395,7 +395,20 @@ def run_gpu_arm(args, cfg, workload):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # NCCL may print a version banner on stdout while the communicator comes up; stdout is
+        # reserved for the one JSON line, so it is pointed at stderr during initialisation.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device)
+            warm = torch.zeros(1, device=device)
+            dist.all_reduce(warm)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     pkg = load_package()
     from hands_on_mlir_b200.bert_program import BertProgram, shard_batch
