@@ -46,6 +46,32 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
   return fmaf(fabsf(x), g, 0.5f * x);
 }
 
+// The same GELU on two values at once with the packed fp32 FMA/MUL of sm_100
+// (fma.rn.f32x2): 9 instructions per element instead of 14.
+__device__ __forceinline__ float2 gelu_erf_fast2(float2 x) {
+  const float2 ax = make_float2(fabsf(x.x), fabsf(x.y));
+  const float2 az = __fmul2_rn(ax, make_float2(0.70710678118654752f, 0.70710678118654752f));
+  const float2 d = __ffma2_rn(make_float2(0.3275911f, 0.3275911f), az, make_float2(1.0f, 1.0f));
+  float2 t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(d.y));
+  // negated, halved coefficients: q = -erfc(z) / (2 exp(-z^2))
+  float2 q = make_float2(-0.5307027145f, -0.5307027145f);
+  q = __ffma2_rn(q, t, make_float2(0.7265760135f, 0.7265760135f));
+  q = __ffma2_rn(q, t, make_float2(-0.7107068705f, -0.7107068705f));
+  q = __ffma2_rn(q, t, make_float2(0.142248368f, 0.142248368f));
+  q = __ffma2_rn(q, t, make_float2(-0.127414796f, -0.127414796f));
+  q = __fmul2_rn(q, t);
+  // exp(-z^2) = 2^(-(|x| k)^2), k = sqrt(log2(e) / 2)
+  const float2 u = __fmul2_rn(ax, make_float2(0.84932180028801904f, 0.84932180028801904f));
+  const float2 w = __fmul2_rn(u, u);
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(-w.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(-w.y));
+  const float2 g = __ffma2_rn(q, e, make_float2(0.5f, 0.5f));  // 1/2 - erfc/2
+  return __ffma2_rn(ax, g, __fmul2_rn(x, make_float2(0.5f, 0.5f)));
+}
+
 // One output row segment of 32 columns held by one thread: `acc` are the raw fp32
 // accumulator bits read from tensor memory.  Columns at or beyond N are not touched
 // (N is a multiple of 8, so whole 8-column groups are either valid or not).
@@ -159,26 +185,17 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
     __syncwarp();
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
-      float v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = ep.alpha * __uint_as_float(acc[g >> 2][(g & 3) * 8 + j]);
-      if (ep.c_mode != 0) {
-        const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[g]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __half22float2(h2[j]);
-          v[2 * j] = fmaf(ep.beta, f.x, v[2 * j]);
-          v[2 * j + 1] = fmaf(ep.beta, f.y, v[2 * j + 1]);
-        }
-      }
-      if (ep.act == 1) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = gelu_erf_fast(v[j]);
-      }
+      const float2 alpha2 = make_float2(ep.alpha, ep.alpha), beta2 = make_float2(ep.beta, ep.beta);
+      const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[g]);
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        const int i0 = (g & 3) * 8 + 2 * j;
+        float2 v = __fmul2_rn(alpha2, make_float2(__uint_as_float(acc[g >> 2][i0]),
+                                                  __uint_as_float(acc[g >> 2][i0 + 1])));
+        if (ep.c_mode != 0) v = __ffma2_rn(beta2, __half22float2(h2[j]), v);
+        if (ep.act == 1) v = gelu_erf_fast2(v);
+        const __half2 h = __floats2half2_rn(v.x, v.y);
         w[j] = *reinterpret_cast<const uint32_t *>(&h);
       }
       const uint32_t addr = my_row + ((static_cast<uint32_t>(g) ^ (lane & 7u)) << 4);
