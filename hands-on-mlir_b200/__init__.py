@@ -208,6 +208,18 @@ class RunnerUtils:
         self._gemm(self.lib.nvteGemmF16, A, B, C, D, transa, transb, activation, alpha, beta,
                    gemmNum, 0)
 
+    def cutlassGemmWithVarMeanF16(self, A, B, C, D, Var, Mean, alpha=1.0, beta=0.0, activation=0,
+                                  eps=1e-5):
+        self.lib.cutlassGemmWithVarMeanF16(*_as_args(A), *_as_args(B), *_as_args(C), *_as_args(D),
+                                           *_as_args(Var), *_as_args(Mean), alpha, beta, activation,
+                                           eps)
+        self.check()
+
+    def cutlassLayernormGemmF16(self, A, B, C, D, Var, Mean, alpha=1.0, beta=0.0, activation=0):
+        self.lib.cutlassLayernormGemmF16(*_as_args(A), *_as_args(B), *_as_args(C), *_as_args(D),
+                                         *_as_args(Var), *_as_args(Mean), alpha, beta, activation)
+        self.check()
+
     def nvteLayernormF16(self, A, eps=1e-6):
         self.lib.nvteLayernormF16(*_as_args(A), eps)
         self.check()

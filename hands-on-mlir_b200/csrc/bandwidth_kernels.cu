@@ -161,6 +161,73 @@ layernorm_generic_kernel(const T *x, const T *res,
   }
 }
 
+// ------------------------------------------------ LayerNorm statistics for the fused forms
+
+// One warp per row of x [rows, n]: rstd = 1 / sqrt(E[x^2] - mean^2 + eps) and
+// shift = -mean * rstd, stored as fp16 like the reference's finaliser
+// (include/NVGPUKernels/Layernorm.h:107-194).
+__global__ void __launch_bounds__(128)
+row_stats_f16_kernel(const __half *x, __half *rstd_out, __half *shift_out, long long rows, int n,
+                     float eps) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __half *xr = x + row * n;
+  float sum = 0.f, sq = 0.f;
+  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(xr) & 15u) == 0) {
+    const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+    for (int i = lane; i < (n >> 3); i += 32) {
+      const uint4 raw = xv[i];
+      const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h2[j]);
+        sum += f.x + f.y;
+        sq = fmaf(f.x, f.x, fmaf(f.y, f.y, sq));
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) {
+      const float f = __half2float(xr[i]);
+      sum += f;
+      sq = fmaf(f, f, sq);
+    }
+  }
+  sum = warp_sum(sum);
+  sq = warp_sum(sq);
+  if (lane == 0) {
+    const float inv_n = 1.f / static_cast<float>(n);
+    const float mean = sum * inv_n;
+    const float rstd = rsqrtf(sq * inv_n - mean * mean + eps);
+    rstd_out[row] = __float2half_rn(rstd);
+    shift_out[row] = __float2half_rn(-mean * rstd);
+  }
+}
+
+// out[n] = sum_k b[k, n] (b is [K, N]) or sum_k b[n, k] (b is [N, K]), fp32.
+__global__ void __launch_bounds__(256)
+col_sum_f16_kernel(const __half *b, float *out, int k_dim, int n_dim, int b_is_nk) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
+  if (b_is_nk) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= n_dim) return;
+    float s = 0.f;
+    for (int k = lane; k < k_dim; k += 32) s += __half2float(b[static_cast<long long>(n) * k_dim + k]);
+    s = warp_sum(s);
+    if (lane == 0) out[n] = s;
+  } else {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= n_dim) return;
+    float s = 0.f;
+    for (int k = 0; k < k_dim; ++k) s += __half2float(b[static_cast<long long>(k) * n_dim + n]);
+    out[n] = s;
+  }
+}
+
 // -------------------------------------------------------------- elementwise
 
 template <int OP>
@@ -437,6 +504,27 @@ bool elementwise(int op, bool is_f16, const void *a, const void *b, void *out, i
     case 2: return elementwise_dispatch<2>(is_f16, a, b, out, n, b_period, sh, stream);
     default: return elementwise_dispatch<3>(is_f16, a, b, out, n, b_period, sh, stream);
   }
+}
+
+bool row_stats_f16(const __half *x, __half *rstd_out, __half *shift_out, int64_t rows, int64_t n,
+                   float eps, cudaStream_t stream) {
+  if (rows == 0 || n == 0) return true;
+  LaunchScope scope(kOpLayernorm, 0.0, 2.0 * rows * n + 4.0 * rows);
+  const unsigned blocks = static_cast<unsigned>((rows + 3) / 4);
+  return check_cuda(launch_pdl(row_stats_f16_kernel, dim3(blocks), dim3(128), 0, stream, 1, x, rstd_out,
+                               shift_out, static_cast<long long>(rows), static_cast<int>(n), eps),
+                    "row statistics kernel launch");
+}
+
+bool col_sum_f16(const __half *b, float *out, int64_t k_dim, int64_t n_dim, bool b_is_nk,
+                 cudaStream_t stream) {
+  if (n_dim == 0) return true;
+  LaunchScope scope(kOpElementwise, 0.0, 2.0 * k_dim * n_dim + 4.0 * n_dim);
+  const unsigned blocks = b_is_nk ? static_cast<unsigned>((n_dim + 7) / 8)
+                                  : static_cast<unsigned>((n_dim + 255) / 256);
+  return check_cuda(launch_pdl(col_sum_f16_kernel, dim3(blocks), dim3(256), 0, stream, 1, b, out,
+                               static_cast<int>(k_dim), static_cast<int>(n_dim), b_is_nk ? 1 : 0),
+                    "column sum kernel launch");
 }
 
 bool gather_rows(bool is_f16, const int64_t *idx, const void *table, void *out, int64_t rows,

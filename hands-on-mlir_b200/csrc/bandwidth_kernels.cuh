@@ -20,6 +20,13 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
 bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, float eps,
                    cudaStream_t stream);
 
+// rstd_out[r] = 1 / sqrt(E[x^2] - mean^2 + eps), shift_out[r] = -mean * rstd over each row of x.
+bool row_stats_f16(const __half *x, __half *rstd_out, __half *shift_out, int64_t rows, int64_t n,
+                   float eps, cudaStream_t stream);
+// out[n] = sum over k of B[k, n] (or B[n, k] when b_is_nk), fp32.
+bool col_sum_f16(const __half *b, float *out, int64_t k_dim, int64_t n_dim, bool b_is_nk,
+                 cudaStream_t stream);
+
 // op: 0 add, 1 sub, 2 mul, 3 div.  b_period > 0 means B repeats every b_period elements of
 // the flat output (leading-dimension broadcast or no broadcast); otherwise `sh` is used.
 bool elementwise(int op, bool is_f16, const void *a, const void *b, void *out, int64_t n,

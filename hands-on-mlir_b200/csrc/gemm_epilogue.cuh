@@ -21,6 +21,12 @@ struct EpilogueParams {
   float alpha, beta;
   int act;  // 1: erf GELU
   int M, N;
+  // Optional LayerNorm-on-A form: the accumulator holds A.B for the raw A and the epilogue
+  // applies acc <- row_scale[r] * acc + row_shift[r] * col_sum[n], which equals
+  // (A * row_scale + row_shift).B.  All three null when unused.
+  const __half *row_scale;
+  const __half *row_shift;
+  const float *col_sum;
 };
 
 // GELU(x) = x * Phi(x) with erf from the rational-times-exponential form
@@ -179,6 +185,16 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
       tc_fence_before_sync();
       __syncwarp();
       release();
+    }
+    if (ep.row_scale != nullptr) {
+      const bool row_in = row < ep.M;
+      const float rs = row_in ? __half2float(ep.row_scale[row]) : 0.f;
+      const float sh = row_in ? __half2float(ep.row_shift[row]) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float cs = c0 + i < ep.N ? ep.col_sum[c0 + i] : 0.f;
+        acc[i >> 5][i & 31] = __float_as_uint(fmaf(rs, __uint_as_float(acc[i >> 5][i & 31]), sh * cs));
+      }
     }
     // This staging tile was last handed to TMA two stores ago: that read must be over.
     if (lane == 0) bulk_wait_group_read_1();

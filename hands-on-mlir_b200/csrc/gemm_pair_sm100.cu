@@ -352,6 +352,9 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   p.ep.alpha = pb.alpha;
   p.ep.beta = pb.beta;
   p.ep.act = pb.act;
+  p.ep.row_scale = pb.row_scale;
+  p.ep.row_shift = pb.row_shift;
+  p.ep.col_sum = pb.col_sum;
   p.ep.M = static_cast<int>(pb.M);
   p.ep.N = static_cast<int>(pb.N);
   p.K = static_cast<int>(pb.K);

@@ -498,6 +498,9 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
   p.ep.alpha = pb.alpha;
   p.ep.beta = pb.beta;
   p.ep.act = pb.act;
+  p.ep.row_scale = pb.row_scale;
+  p.ep.row_shift = pb.row_shift;
+  p.ep.col_sum = pb.col_sum;
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
   p.num_tiles = m_blocks * p.n_blocks;

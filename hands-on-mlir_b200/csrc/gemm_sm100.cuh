@@ -18,6 +18,11 @@ struct Problem {
   __half *D = nullptr;
   float alpha = 1.f, beta = 0.f;
   int act = 0;  // 1 = erf GELU
+  // LayerNorm-on-A form (all null when unused): D = epilogue(alpha * (A * row_scale + row_shift).B ...)
+  // evaluated as row_scale[r] * (A.B)[r,n] + row_shift[r] * col_sum[n] with col_sum = column sums of B.
+  const __half *row_scale = nullptr;
+  const __half *row_shift = nullptr;
+  const float *col_sum = nullptr;
 };
 
 // Enqueues the GEMM; tile_row 1..4 forces one CTA per 128 x {64,128,192,256} tile, 5..6 one

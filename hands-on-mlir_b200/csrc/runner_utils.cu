@@ -154,67 +154,72 @@ void dealloc_memref(int64_t rank, void *dst) {
   if (data) hom::check_cuda(cudaFree(data), "cudaFree");
 }
 
-// Shared front end of cutlassGemmF16 / nvteGemmF16.
-void gemm_entry(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64_t rankB,
-                void *dstB, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
-                int64_t activation, float alpha, float beta, int32_t tile_row) {
+// Validates the operands of a GEMM entry point and fills `out`; returns false when the call
+// is rejected (error recorded) or there is nothing to do (M or N is 0: *empty set).
+bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64_t rankB,
+                  void *dstB, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                  int64_t activation, float alpha, float beta, hom::gemm::Problem *out, bool *empty) {
+  *empty = false;
   MemRefView A = view_memref(rankA, dstA, 2), B = view_memref(rankB, dstB, 2);
   MemRefView C = view_memref(rankC, dstC, 2), D = view_memref(rankD, dstD, 2);
   if (!A.valid || !B.valid || !D.valid) {
     set_error(HOM_ERR_INVALID, "%s: null or malformed A/B/D descriptor", name);
-    return;
+    return false;
   }
   if ((A.rank != 2 && A.rank != 3) || (B.rank != 2 && B.rank != 3) || D.rank != A.rank) {
     set_error(HOM_ERR_INVALID, "%s: A, D must be rank 2 or 3 and B rank 2 or 3", name);
-    return;
+    return false;
   }
   if (!A.contiguous() || !B.contiguous() || !D.contiguous()) {
     set_error(HOM_ERR_INVALID, "%s: operands must be row-major contiguous", name);
-    return;
+    return false;
   }
   if (activation != 0 && activation != 1) {
     set_error(HOM_ERR_UNSUPPORTED, "%s: activation %lld (0 = none, 1 = erf GELU)", name,
               static_cast<long long>(activation));
-    return;
+    return false;
   }
   const int64_t K = A.sizes[A.rank - 1];
   const int64_t M = A.numel() / (K ? K : 1);
   if (B.rank == 3 && B.sizes[0] != 1) {
     set_error(HOM_ERR_UNSUPPORTED, "%s: B must have batch 1 (weights are shared by the batch)", name);
-    return;
+    return false;
   }
   const int64_t b0 = B.sizes[B.rank - 2], b1 = B.sizes[B.rank - 1];
   const int64_t Kb = b_is_nk ? b1 : b0, N = b_is_nk ? b0 : b1;
   if (Kb != K) {
     set_error(HOM_ERR_INVALID, "%s: inner dimensions differ (A has K=%lld, B has K=%lld)", name,
               static_cast<long long>(K), static_cast<long long>(Kb));
-    return;
+    return false;
   }
   if (D.sizes[D.rank - 1] != N || D.numel() != M * N) {
     set_error(HOM_ERR_INVALID, "%s: D must be [%lld x %lld]", name, static_cast<long long>(M),
               static_cast<long long>(N));
-    return;
+    return false;
   }
   for (int64_t i = 0; i + 1 < A.rank; ++i) {
     if (A.sizes[i] != D.sizes[i]) {
       set_error(HOM_ERR_INVALID, "%s: leading dimensions of A and D differ", name);
-      return;
+      return false;
     }
   }
-  if (M == 0 || N == 0) return;
+  if (M == 0 || N == 0) {
+    *empty = true;
+    return false;
+  }
   if (K == 0) {
     set_error(HOM_ERR_UNSUPPORTED, "%s: K == 0", name);
-    return;
+    return false;
   }
   if (K % 8 != 0 || N % 8 != 0) {
     set_error(HOM_ERR_UNSUPPORTED,
               "%s: K and N must be multiples of 8 (16-byte rows for TMA); got K=%lld N=%lld", name,
               static_cast<long long>(K), static_cast<long long>(N));
-    return;
+    return false;
   }
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) {
     set_error(HOM_ERR_UNSUPPORTED, "%s: dimension exceeds 2^31-1", name);
-    return;
+    return false;
   }
   hom::gemm::Problem pb;
   pb.M = M;
@@ -231,7 +236,7 @@ void gemm_entry(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64
   if (beta != 0.f) {
     if (!C.valid || !C.contiguous()) {
       set_error(HOM_ERR_INVALID, "%s: beta != 0 needs a contiguous C", name);
-      return;
+      return false;
     }
     if (C.numel() == M * N && C.sizes[C.rank - 1] == N) {
       pb.c_mode = 1;
@@ -240,20 +245,65 @@ void gemm_entry(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64
     } else {
       set_error(HOM_ERR_INVALID, "%s: C must be [%lld x %lld] or a length-%lld row", name,
                 static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(N));
-      return;
+      return false;
     }
     pb.C = reinterpret_cast<const __half *>(C.ptr);
     if (!is_aligned16(pb.C)) {
       set_error(HOM_ERR_INVALID, "%s: C is not 16-byte aligned", name);
-      return;
+      return false;
     }
   }
   if (!is_aligned16(pb.A) || !is_aligned16(pb.B) || !is_aligned16(pb.D)) {
     set_error(HOM_ERR_INVALID, "%s: A, B and D must be 16-byte aligned", name);
-    return;
+    return false;
   }
+  *out = pb;
+  return true;
+}
+
+// Shared front end of cutlassGemmF16 / nvteGemmF16.
+void gemm_entry(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64_t rankB,
+                void *dstB, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                int64_t activation, float alpha, float beta, int32_t tile_row) {
+  hom::gemm::Problem pb;
+  bool empty = false;
+  if (!gemm_prepare(name, b_is_nk, rankA, dstA, rankB, dstB, rankC, dstC, rankD, dstD, activation,
+                    alpha, beta, &pb, &empty))
+    return;
   hom::gemm::run(pb, tile_row, hom::current_stream());
 }
+
+// Library-owned scratch for the column sums of B that the LayerNorm-on-A GEMM needs: one
+// fixed buffer per device, allocated on first use (the reference keeps grow-only static device
+// scratch for the same kind of purpose, include/NVGPUKernels/Utils.h:179-224).
+constexpr int64_t kColSumCapacity = 65536;
+float *col_sum_scratch() {
+  static float *bufs[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!bufs[dev]) {
+    void *ptr = nullptr;
+    if (!hom::check_cuda(cudaMalloc(&ptr, kColSumCapacity * sizeof(float)), "cudaMalloc(column sums)"))
+      return nullptr;
+    bufs[dev] = static_cast<float *>(ptr);
+  }
+  return bufs[dev];
+}
+
+// Var / Mean operands of the fused forms: rank-1 fp16 with at least `rows` entries.
+bool stats_operand(const char *name, const char *what, int64_t rank, void *dst, int64_t rows,
+                   __half **out) {
+  MemRefView v = view_memref(rank, dst, 2);
+  if (!v.valid || v.rank != 1 || v.sizes[0] < rows || !v.contiguous()) {
+    set_error(HOM_ERR_INVALID, "%s: %s must be a rank-1 fp16 memref with at least %lld entries", name,
+              what, static_cast<long long>(rows));
+    return false;
+  }
+  *out = reinterpret_cast<__half *>(v.ptr);
+  return true;
+}
+
 
 void elementwise_entry(const char *name, int op, bool is_f16, int64_t rankA, void *dstA,
                        int64_t rankB, void *dstB, int64_t rankOut, void *dstOut) {
@@ -401,10 +451,25 @@ void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *ds
              alpha, beta, gemmNum);
 }
 
-void cutlassGemmWithVarMeanF16(int64_t, void *, int64_t, void *, int64_t, void *, int64_t, void *,
-                               int64_t, void *, int64_t, void *, float, float, int64_t, float) {
-  set_error(HOM_ERR_UNSUPPORTED,
-            "cutlassGemmWithVarMeanF16: GEMM + row-statistics fusion is not built yet");
+void cutlassGemmWithVarMeanF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB, int64_t rankC,
+                               void *dstC, int64_t rankD, void *dstD, int64_t rankVar, void *dstVar,
+                               int64_t rankMean, void *dstMean, float alpha, float beta,
+                               int64_t activation, float eps) {
+  // D = alpha * A.B + beta * C, then per row of D: Var <- 1/sqrt(E[x^2] - mean^2 + eps) and
+  // Mean <- -mean * Var (what the reference leaves in its first Bs*M entries after
+  // ApplyFinalReduction).  `activation` is ignored, as in the reference.
+  (void)activation;
+  hom::gemm::Problem pb;
+  bool empty = false;
+  if (!gemm_prepare("cutlassGemmWithVarMeanF16", false, rankA, dstA, rankB, dstB, rankC, dstC, rankD,
+                    dstD, 0, alpha, beta, &pb, &empty))
+    return;
+  __half *var = nullptr, *mean = nullptr;
+  if (!stats_operand("cutlassGemmWithVarMeanF16", "Var", rankVar, dstVar, pb.M, &var) ||
+      !stats_operand("cutlassGemmWithVarMeanF16", "Mean", rankMean, dstMean, pb.M, &mean))
+    return;
+  if (!hom::gemm::run(pb, 0, hom::current_stream())) return;
+  hom::bw::row_stats_f16(pb.D, var, mean, pb.M, pb.N, eps, hom::current_stream());
 }
 
 void cutlassLayernormGemmF32(int64_t, void *, int64_t, void *, int64_t, void *, int64_t, void *,
@@ -412,10 +477,35 @@ void cutlassLayernormGemmF32(int64_t, void *, int64_t, void *, int64_t, void *, 
   set_error(HOM_ERR_UNSUPPORTED, "cutlassLayernormGemmF32: empty stub in the reference");
 }
 
-void cutlassLayernormGemmF16(int64_t, void *, int64_t, void *, int64_t, void *, int64_t, void *,
-                             int64_t, void *, int64_t, void *, float, float, int64_t) {
-  set_error(HOM_ERR_UNSUPPORTED,
-            "cutlassLayernormGemmF16: LayerNorm-on-load GEMM fusion is not built yet");
+void cutlassLayernormGemmF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB, int64_t rankC,
+                             void *dstC, int64_t rankD, void *dstD, int64_t rankVar, void *dstVar,
+                             int64_t rankMean, void *dstMean, float alpha, float beta,
+                             int64_t activation) {
+  // D = alpha * (A * Var[r] + Mean[r]).B + beta * C with the row statistics a preceding
+  // cutlassGemmWithVarMeanF16 produced (LayerNorm of A with scale 1, shift 0).  The GEMM runs
+  // on the raw A; the epilogue applies Var[r] * acc + Mean[r] * colsum(B)[n].
+  (void)activation;
+  hom::gemm::Problem pb;
+  bool empty = false;
+  if (!gemm_prepare("cutlassLayernormGemmF16", false, rankA, dstA, rankB, dstB, rankC, dstC, rankD,
+                    dstD, 0, alpha, beta, &pb, &empty))
+    return;
+  __half *var = nullptr, *mean = nullptr;
+  if (!stats_operand("cutlassLayernormGemmF16", "Var", rankVar, dstVar, pb.M, &var) ||
+      !stats_operand("cutlassLayernormGemmF16", "Mean", rankMean, dstMean, pb.M, &mean))
+    return;
+  if (pb.N > kColSumCapacity) {
+    set_error(HOM_ERR_UNSUPPORTED, "cutlassLayernormGemmF16: N = %lld exceeds the %lld-column scratch",
+              static_cast<long long>(pb.N), static_cast<long long>(kColSumCapacity));
+    return;
+  }
+  float *col_sum = col_sum_scratch();
+  if (!col_sum) return;
+  if (!hom::bw::col_sum_f16(pb.B, col_sum, pb.K, pb.N, false, hom::current_stream())) return;
+  pb.row_scale = var;
+  pb.row_shift = mean;
+  pb.col_sum = col_sum;
+  hom::gemm::run(pb, 0, hom::current_stream());
 }
 
 void nvteLayernormF16(int64_t rankA, void *dstA, float eps) {

@@ -68,9 +68,15 @@ HOM_EXPORT void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rank
                             int64_t activation, float alpha, float beta, int32_t gemmNum,
                             int32_t unused);
 
-/* GEMM whose epilogue also emits per-row partial statistics, and the GEMM that consumes
- * them (HandsOnNVGPURunnerUtils.cu:118-170, :191-222).  Not emitted by the compiler for
- * BERT; exported for link parity. */
+/* The GEMM <-> LayerNorm-statistics pair (HandsOnNVGPURunnerUtils.cu:118-170, :191-222;
+ * include/NVGPUKernels/LayernormGemmRunner.h, Layernorm.h:107-194).
+ * cutlassGemmWithVarMeanF16: D = alpha * A.B + beta * C, then for every row r of D
+ *   Var[r] = 1 / sqrt(E[x^2] - mean^2 + eps), Mean[r] = -mean * Var[r]   (fp16, rank 1,
+ *   at least Bs*M entries; `activation` is ignored as in the reference).
+ * cutlassLayernormGemmF16: D = alpha * (A * Var[r] + Mean[r]).B + beta * C, i.e. the GEMM of
+ *   the LayerNorm of A (scale 1, shift 0) with those statistics.
+ * Neither is emitted by the compiler for BERT.  cutlassLayernormGemmF32 is an empty stub in
+ * the reference and records "unsupported". */
 HOM_EXPORT void cutlassGemmWithVarMeanF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
                                           int64_t rankC, void *dstC, int64_t rankD, void *dstD,
                                           int64_t rankVar, void *dstVar, int64_t rankMean,

@@ -86,6 +86,35 @@ def layernorm_f16(x, eps, res=None, gamma=None, beta=None):
     return out
 
 
+def row_stats_f16(x, eps):
+    """(rstd, shift) per row of x, fp16: the Var / Mean outputs of cutlassGemmWithVarMeanF16."""
+    x = _f16(x)
+    n = x.shape[-1]
+    rows = x.size // n
+    rstd = np.empty(rows, dtype=np.float16)
+    shift = np.empty(rows, dtype=np.float16)
+    lib().oracle_row_stats_f16(_p(x), _p(rstd), _p(shift), c_int64(rows), c_int64(n), c_float(eps))
+    return rstd, shift
+
+
+def layernorm_gemm_f16(A, rstd, shift, B, C=None, *, alpha=1.0, beta=0.0):
+    """D = alpha * (A * rstd[r] + shift[r]).B + beta * C  (cutlassLayernormGemmF16)."""
+    A, B = _f16(A), _f16(B)
+    K = A.shape[-1]
+    M = A.size // K
+    B2 = B.reshape(B.shape[-2], B.shape[-1])
+    N = B2.shape[1]
+    c_mode = 0
+    if C is not None and beta != 0.0:
+        C = _f16(C)
+        c_mode = 1 if C.size == M * N else 2
+    D = np.empty(A.shape[:-1] + (N,), dtype=np.float16)
+    lib().oracle_layernorm_gemm_f16(_p(A), _p(_f16(rstd)), _p(_f16(shift)), _p(B2),
+                                    _p(C) if c_mode else None, c_int(c_mode), _p(D), c_int64(M),
+                                    c_int64(N), c_int64(K), c_float(alpha), c_float(beta))
+    return D
+
+
 def layernorm_f32(x, eps):
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = np.empty_like(x)

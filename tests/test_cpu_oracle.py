@@ -35,6 +35,25 @@ def test_verify_py_gemm_ln_gemm_chain(oracle):
     np.testing.assert_allclose(-mean / np.sqrt(sq - mean * mean + 1e-5), g["shift"], rtol=1e-4)
 
 
+def test_fused_statistics_pair_against_verify_py(oracle):
+    """row_stats + layernorm_gemm (the cutlassGemmWithVarMeanF16 / cutlassLayernormGemmF16 pair)
+    against verify.py's rstd, -mean*rstd and LN(A.B).C; the statistics are fp16 like the
+    reference's, which bounds the accuracy of the second product."""
+    g = np.load(GOLDEN / "verify_gemm_ln_gemm.npz")
+    ab = oracle.gemm_f16(f16(g["a"])[None], f16(g["b"])[None])
+    rstd, shift = oracle.row_stats_f16(ab, 1e-5)
+    assert_close_f16(rstd, g["rstd"], "rstd", rtol=2e-3, atol=2e-3)
+    assert_close_f16(shift, g["shift"], "shift", rtol=2e-3, atol=8e-3)
+    d2 = oracle.layernorm_gemm_f16(ab, rstd, shift, f16(g["c"])[None])
+    assert_close_f16(d2[0], g["ln_ab_c"], "LN(A.B).C", rtol=1e-2, atol=4e-2)
+    # with exact fp32 statistics the same formula reproduces the golden values tightly
+    abf = ab[0].astype(np.float64)
+    mean, sq = abf.mean(-1), (abf * abf).mean(-1)
+    r = 1 / np.sqrt(sq - mean * mean + 1e-6)
+    want = ((abf - mean[:, None]) * r[:, None]) @ g["c"].astype(np.float64)
+    np.testing.assert_allclose(want, g["ln_ab_c"], rtol=5e-3, atol=5e-3)
+
+
 def test_gemm_against_torch_fixture(oracle):
     g = np.load(GOLDEN / "torch_ops.npz")
     A, B, bias = g["gemm_A"], g["gemm_B"], g["gemm_bias"]
