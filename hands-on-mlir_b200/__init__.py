@@ -136,6 +136,7 @@ _SIGNATURES = {
     "homSynchronize": (ctypes.c_int, []),
     "homSetConstantDir": (None, [c_char_p]),
     "homResidualLayernormF16": (None, _MEMREF * 5 + [c_float]),
+    "homLayernormGemmF16NoAlloc": (None, _MEMREF * 6 + [c_float, c_float]),
     "homKernelLaunchCount": (c_int64, []),
     "homOpTimingEnable": (None, [ctypes.c_int]),
     "homOpTimingCollect": (c_int64, [ctypes.POINTER(OpTiming), c_int64]),
@@ -218,6 +219,11 @@ class RunnerUtils:
     def cutlassLayernormGemmF16(self, A, B, C, D, Var, Mean, alpha=1.0, beta=0.0, activation=0):
         self.lib.cutlassLayernormGemmF16(*_as_args(A), *_as_args(B), *_as_args(C), *_as_args(D),
                                          *_as_args(Var), *_as_args(Mean), alpha, beta, activation)
+        self.check()
+
+    def homLayernormGemmF16NoAlloc(self, A, B, C, D, Var, Mean, alpha=1.0, beta=0.0):
+        self.lib.homLayernormGemmF16NoAlloc(*_as_args(A), *_as_args(B), *_as_args(C), *_as_args(D),
+                                            *_as_args(Var), *_as_args(Mean), alpha, beta)
         self.check()
 
     def nvteLayernormF16(self, A, eps=1e-6):

@@ -36,6 +36,7 @@ RUNNER_SOURCES = [
     "attention_sm100.cu",
     "bandwidth_kernels.cu",
     "runner_utils.cu",
+    "no_alloc_entry.cu",
 ]
 REPLAY_SOURCES = ["bert_replay.cpp"]
 

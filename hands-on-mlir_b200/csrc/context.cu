@@ -85,6 +85,13 @@ bool pdl_enabled() {
 
 int *device_status_word() { return device_state().status_dev; }
 
+int *device_status_word_if_ready() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  return g_devices[dev].status_dev;  // null until some earlier call initialised this device
+}
+
 int sm_count() {
   int n = device_state().sm_count;
   return n > 0 ? n : 148;

@@ -556,6 +556,105 @@ const ShapeRow kShapeTable[] = {
 
 }  // namespace
 
+namespace {
+
+// cuTensorMapEncodeTiled without the cache (no host allocation either).
+bool encode_map_uncached(const void *ptr, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
+                         const cuuint32_t *box, CUtensorMap *out) {
+  EncodeFn encode = get_encode_fn();
+  if (!encode) {
+    set_error(HOM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank),
+                            const_cast<void *>(ptr), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(HOM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    return false;
+  }
+  return true;
+}
+
+}  // namespace
+
+// Launches the 128 x 128 single-CTA kernel for `pb` (B as [K, N]) without allocating anything:
+// tensor maps are encoded on the stack instead of being cached, the device status word is used
+// only if an earlier call already created it, and the SM count comes straight from the
+// device attribute.
+bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
+  constexpr int BN = 128;
+  using Cfg = TileCfg<BN>;
+  if (pb.M == 0 || pb.N == 0) return true;
+  auto kernel = gemm_f16_kernel<BN, false>;
+  if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::kSmemBytes),
+                  "cudaFuncSetAttribute(gemm)"))
+    return false;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  CUtensorMap tmA, tmB, tmD;
+  const bool grouped = pb.N % 64 == 0;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(pb.K), static_cast<cuuint64_t>(pb.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pb.K) * 2};
+    const cuuint32_t box[2] = {BK, BM};
+    if (!encode_map_uncached(pb.A, 2, dims, strides, box, &tmA)) return false;
+  }
+  if (grouped) {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(pb.K), static_cast<cuuint64_t>(pb.N / 64)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(pb.N) * 2, 128};
+    const cuuint32_t box[3] = {64, BK, BN / 64};
+    if (!encode_map_uncached(pb.B, 3, dims, strides, box, &tmB)) return false;
+  } else {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(pb.N), static_cast<cuuint64_t>(pb.K)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pb.N) * 2};
+    const cuuint32_t box[2] = {64, BK};
+    if (!encode_map_uncached(pb.B, 2, dims, strides, box, &tmB)) return false;
+  }
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(pb.N), static_cast<cuuint64_t>(pb.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pb.N) * 2};
+    const cuuint32_t box[2] = {64, 32};
+    if (!encode_map_uncached(pb.D, 2, dims, strides, box, &tmD)) return false;
+  }
+  Params p;
+  p.ep.M = static_cast<int>(pb.M);
+  p.ep.N = static_cast<int>(pb.N);
+  p.K = static_cast<int>(pb.K);
+  p.ep.C = pb.C;
+  p.ep.ldc = pb.N;
+  p.ep.c_mode = pb.c_mode;
+  p.ep.D = pb.D;
+  p.ep.ldd = pb.N;
+  p.ep.alpha = pb.alpha;
+  p.ep.beta = pb.beta;
+  p.ep.act = pb.act;
+  p.ep.row_scale = pb.row_scale;
+  p.ep.row_shift = pb.row_shift;
+  p.ep.col_sum = pb.col_sum;
+  p.b_grouped = grouped ? 1 : 0;
+  const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
+  p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
+  p.num_tiles = m_blocks * p.n_blocks;
+  p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
+  p.stages = Cfg::kStages;
+  p.status = device_status_word_if_ready();
+  p.prof = nullptr;
+  const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  const double flops = 2.0 * pb.M * pb.N * pb.K;
+  const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
+                              static_cast<double>(pb.M) * pb.N);
+  LaunchScope scope(kOpGemm, flops, bytes);
+  return check_cuda(launch_pdl(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, 1, tmA, tmB,
+                               tmD, p),
+                    "gemm kernel launch");
+}
+
 int select_tile_row(int64_t m, int64_t n, int64_t k, int act) {
   if (const char *env = std::getenv("HOM_GEMM_TILE")) {  // experiment knob
     const int v = std::atoi(env);

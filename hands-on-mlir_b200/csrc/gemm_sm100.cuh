@@ -32,6 +32,10 @@ bool run(const Problem &pb, int tile_row, cudaStream_t stream);
 // The CTA-pair kernels (gemm_pair_sm100.cu); bn2 is 128 or 256.
 bool run_pair(const Problem &pb, int bn2, cudaStream_t stream);
 
+// The 128 x 128 single-CTA kernel for `pb` (B as [K, N]) launched without any allocation (no
+// tensor-map cache insert, no status-word creation).
+bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream);
+
 int select_tile_row(int64_t m, int64_t n, int64_t k, int act);
 int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, int *split_k);
 

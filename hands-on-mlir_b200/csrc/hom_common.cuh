@@ -77,6 +77,9 @@ cudaStream_t current_stream();
 bool pdl_enabled();
 // Host-mapped status word that device code writes on a bounded-wait expiry (device pointer).
 int *device_status_word();
+// The same pointer if an earlier call on this device already created it, else null; never
+// allocates.
+int *device_status_word_if_ready();
 int sm_count();
 
 // Launches `kernel` with programmatic stream serialization allowed (and, when cluster_x > 1,

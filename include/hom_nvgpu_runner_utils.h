@@ -192,6 +192,26 @@ HOM_EXPORT void homResidualLayernormF16(int64_t rankX, void *dstX, int64_t rankR
                                         int64_t rankGamma, void *dstGamma, int64_t rankBeta,
                                         void *dstBeta, int64_t rankOut, void *dstOut, float eps);
 
+/* cutlassLayernormGemmF16 for callers that must not allocate device memory - a process whose
+ * memory was budgeted once at start-up, a plug-in running under a framework where cudaMalloc
+ * would stall every stream of the device, a latency-critical loop.  Same operands and result:
+ * D = alpha * (A * Var[r] + Mean[r]).B + beta * C (A [Bs,M,K], B [1,K,N], C [Bs,M,N] or
+ * [1,1,N] or unused when beta == 0, D [Bs,M,N], Var/Mean fp16 [>= Bs*M]).  The column sums of
+ * B that the computation needs live in a fixed 64 KB array inside the library image instead
+ * of a cudaMalloc'ed buffer, so N is limited to 16384 columns (larger N: error 2, nothing is
+ * launched) and every GPU that loads the library carries those 64 KB until the process ends.
+ * The call performs no cudaMalloc / cudaFree / cudaHostAlloc and uses no allocating library.
+ * The first call on each device looks up the array's device address (with that device
+ * current); make that first call outside of any stream capture.  All calls share the one
+ * array: each call rewrites the entries it uses before reading them, so nothing needs
+ * clearing between calls, but two calls whose kernels overlap on the GPU (different streams,
+ * or host threads on one device) would overwrite each other's sums - issue them on one stream.
+ * This entry point has no counterpart in the reference. */
+HOM_EXPORT void homLayernormGemmF16NoAlloc(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
+                                           int64_t rankC, void *dstC, int64_t rankD, void *dstD,
+                                           int64_t rankVar, void *dstVar, int64_t rankMean,
+                                           void *dstMean, float alpha, float beta);
+
 /* Number of kernels this library has launched since load (all threads). */
 HOM_EXPORT int64_t homKernelLaunchCount(void);
 
