@@ -183,3 +183,53 @@ class BertProgram:
         rows = torch.arange(b * s, dtype=torch.int64, device="cuda").reshape(b, s)
         self._hom.gather("F16", rows, table, out)
         return out
+
+
+class ModelLibrary:
+    """A model library compiled by Hands-on-MLIR, driven through the LLVM-free loader
+    (homModelOpen / homModelInvoke in include/hom_bert_replay.h)."""
+
+    def __init__(self, so_path):
+        lib = _replay_lib()
+        lib.homModelOpen.restype = c_void_p
+        lib.homModelOpen.argtypes = [ctypes.c_char_p]
+        lib.homModelInvoke.restype = c_int
+        lib.homModelInvoke.argtypes = [c_void_p, ctypes.c_char_p, c_int32, ctypes.POINTER(c_void_p),
+                                       c_void_p]
+        lib.homModelInitTensorCount.restype = c_int32
+        lib.homModelInitTensorCount.argtypes = [c_void_p, ctypes.c_char_p]
+        lib.homModelLastError.restype = ctypes.c_char_p
+        lib.homModelLastError.argtypes = [c_void_p]
+        lib.homModelClose.argtypes = [c_void_p]
+        self._lib = lib
+        self._handle = lib.homModelOpen(str(so_path).encode())
+        if not self._handle:
+            raise OSError(f"cannot load model library {so_path}")
+
+    def invoke(self, fn: str, args, result=None):
+        """`args`: MemRef objects (two slots each) or ctypes scalars (one slot each).
+        Returns the result as an UnrankedMemRef (or fills `result` if given)."""
+        slots, keep = [], []
+        for a in args:
+            if isinstance(a, MemRef):
+                rank, desc = a.args
+                keep += [rank, desc]
+                slots += [ctypes.addressof(rank), ctypes.addressof(desc)]
+            else:
+                keep.append(a)
+                slots.append(ctypes.addressof(a))
+        arr = (c_void_p * max(1, len(slots)))(*slots)
+        res = result if result is not None else UnrankedMemRef()
+        rc = self._lib.homModelInvoke(self._handle, fn.encode(), len(slots), arr, ctypes.byref(res))
+        if rc != 0:
+            runner().check()
+            raise HomError(rc, (self._lib.homModelLastError(self._handle) or b"").decode())
+        return res
+
+    def init_tensor_count(self, fn: str) -> int:
+        return int(self._lib.homModelInitTensorCount(self._handle, fn.encode()))
+
+    def close(self):
+        if self._handle:
+            self._lib.homModelClose(self._handle)
+            self._handle = None

@@ -38,7 +38,7 @@ RUNNER_SOURCES = [
     "runner_utils.cu",
     "no_alloc_entry.cu",
 ]
-REPLAY_SOURCES = ["bert_replay.cpp"]
+REPLAY_SOURCES = ["bert_replay.cpp", "model_loader.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -108,7 +108,8 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
     replay_objs = [objs[n] for n in REPLAY_SOURCES if n in objs]
     if replay_objs and (force or jobs or not REPLAY_LIB.exists()):
         _link(replay_objs, REPLAY_LIB,
-              [f"-L{LIB_DIR}", "-lhands_on_mlir_nvgpu_runner_utils", "-Xlinker", "-rpath=$ORIGIN"],
+              [f"-L{LIB_DIR}", "-lhands_on_mlir_nvgpu_runner_utils", "-ldl", "-Xlinker",
+               "-rpath=$ORIGIN"],
               verbose)
     return {"runner": RUNNER_LIB, "replay": REPLAY_LIB}
 

@@ -27,6 +27,10 @@ struct EpilogueParams {
   const __half *row_scale;
   const __half *row_shift;
   const float *col_sum;
+  // 1 when N is not a multiple of 8: rows of C / D are then not 16-byte aligned, so C is read
+  // element by element and D is written by the warp from its staging tile with 4- or 2-byte
+  // stores instead of a TMA store.
+  int unaligned_n;
 };
 
 // GELU(x) = x * Phi(x) with erf from the rational-times-exponential form
@@ -144,6 +148,12 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
   if (ep.c_mode == 0) return;
   const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
   const bool row_ok = ep.c_mode == 2 || row < ep.M;
+  if (ep.unaligned_n) {
+    __half *dst = reinterpret_cast<__half *>(cval);
+#pragma unroll 8
+    for (int i = 0; i < 64; ++i) dst[i] = (row_ok && c0 + i < ep.N) ? cp[i] : __float2half_rn(0.f);
+    return;
+  }
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
     const bool ok = row_ok && c0 + g * 8 < ep.N;
@@ -219,11 +229,37 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
                    "r"(w[2]), "r"(w[3])
                    : "memory");
     }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, tile, c0, row0);
-      bulk_commit_group();  // one group per step (possibly empty) keeps the tile rotation exact
+    if (!ep.unaligned_n) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, tile, c0, row0);
+        bulk_commit_group();  // one group per step (possibly empty) keeps the tile rotation exact
+      }
+    } else {
+      // Rows of D are not 16-byte aligned: the warp copies its staging tile out row by row,
+      // lane l writing columns c0 + 2l, c0 + 2l + 1 (one 128-byte row segment per instruction).
+      __syncwarp();
+      const int col = c0 + 2 * lane;
+      const uint32_t chunk = static_cast<uint32_t>(lane) >> 2, within = (static_cast<uint32_t>(lane) & 3u) << 2;
+      for (int r = 0; r < 32; ++r) {
+        const int grow = row0 + r;
+        if (grow >= ep.M) break;
+        uint32_t word;
+        asm volatile("ld.shared.b32 %0, [%1];"
+                     : "=r"(word)
+                     : "r"(tile + r * 128 + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4) + within)
+                     : "memory");
+        __half *dp = ep.D + static_cast<long long>(grow) * ep.ldd + col;
+        if (col + 1 < ep.N && (reinterpret_cast<uintptr_t>(dp) & 3u) == 0) {
+          *reinterpret_cast<uint32_t *>(dp) = word;
+        } else {
+          const __half2 h = *reinterpret_cast<const __half2 *>(&word);
+          if (col < ep.N) dp[0] = __low2half(h);
+          if (col + 1 < ep.N) dp[1] = __high2half(h);
+        }
+      }
+      __syncwarp();
     }
     ++n_stores;
   }

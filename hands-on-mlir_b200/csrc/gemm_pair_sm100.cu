@@ -333,7 +333,11 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
 
   CUtensorMap tmA, tmB, tmD;
   if (!make_tensor_map_2d(pb.A, pb.K, pb.M, BK, 128, &tmA)) return false;
-  if (!make_tensor_map_2d(pb.D, pb.N, pb.M, 64, 32, &tmD)) return false;
+  if (pb.N % 8 == 0) {
+    if (!make_tensor_map_2d(pb.D, pb.N, pb.M, 64, 32, &tmD)) return false;
+  } else {
+    tmD = tmA;  // never dereferenced: the epilogue stores without TMA when N % 8 != 0
+  }
   const bool grouped = !B_NK && pb.N % 64 == 0;
   if (B_NK) {
     if (!make_tensor_map_2d(pb.B, pb.K, pb.N, BK, Cfg::kHalfN, &tmB)) return false;
@@ -355,6 +359,7 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   p.ep.row_scale = pb.row_scale;
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
+  p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
   p.ep.M = static_cast<int>(pb.M);
   p.ep.N = static_cast<int>(pb.N);
   p.K = static_cast<int>(pb.K);

@@ -476,7 +476,11 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
   }
   CUtensorMap tmA, tmB, tmD;
   if (!make_tensor_map_2d(pb.A, pb.K, pb.M, BK, BM, &tmA)) return false;
-  if (!make_tensor_map_2d(pb.D, pb.N, pb.M, 64, 32, &tmD)) return false;
+  if (pb.N % 8 == 0) {
+    if (!make_tensor_map_2d(pb.D, pb.N, pb.M, 64, 32, &tmD)) return false;
+  } else {
+    tmD = tmA;  // never dereferenced: the epilogue stores without TMA when N % 8 != 0
+  }
   const bool grouped = !B_NK && pb.N % 64 == 0;
   if (B_NK) {
     if (!make_tensor_map_2d(pb.B, pb.K, pb.N, BK, BN, &tmB)) return false;
@@ -501,6 +505,7 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
   p.ep.row_scale = pb.row_scale;
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
+  p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
   p.num_tiles = m_blocks * p.n_blocks;
@@ -637,6 +642,7 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
   p.ep.row_scale = pb.row_scale;
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
+  p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
   p.b_grouped = grouped ? 1 : 0;
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);

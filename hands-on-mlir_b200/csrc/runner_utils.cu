@@ -211,12 +211,15 @@ bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int
     set_error(HOM_ERR_UNSUPPORTED, "%s: K == 0", name);
     return false;
   }
-  if (K % 8 != 0 || N % 8 != 0) {
+  // TMA needs 16-byte rows: K % 8 == 0 for A (and for B stored [N,K]); N % 8 == 0 for B
+  // stored [K,N].  With B as [N,K] any N works: C / D are then handled without TMA.
+  if (K % 8 != 0 || (!b_is_nk && N % 8 != 0)) {
     set_error(HOM_ERR_UNSUPPORTED,
-              "%s: K and N must be multiples of 8 (16-byte rows for TMA); got K=%lld N=%lld", name,
-              static_cast<long long>(K), static_cast<long long>(N));
+              "%s: K%s must be a multiple of 8 (16-byte rows for TMA); got K=%lld N=%lld", name,
+              b_is_nk ? "" : " and N", static_cast<long long>(K), static_cast<long long>(N));
     return false;
   }
+  const bool unaligned_n = N % 8 != 0;
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) {
     set_error(HOM_ERR_UNSUPPORTED, "%s: dimension exceeds 2^31-1", name);
     return false;
@@ -248,12 +251,12 @@ bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int
       return false;
     }
     pb.C = reinterpret_cast<const __half *>(C.ptr);
-    if (!is_aligned16(pb.C)) {
+    if (!unaligned_n && !is_aligned16(pb.C)) {
       set_error(HOM_ERR_INVALID, "%s: C is not 16-byte aligned", name);
       return false;
     }
   }
-  if (!is_aligned16(pb.A) || !is_aligned16(pb.B) || !is_aligned16(pb.D)) {
+  if (!is_aligned16(pb.A) || !is_aligned16(pb.B) || (!unaligned_n && !is_aligned16(pb.D))) {
     set_error(HOM_ERR_INVALID, "%s: A, B and D must be 16-byte aligned", name);
     return false;
   }

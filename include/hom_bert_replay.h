@@ -77,6 +77,23 @@ HOM_EXPORT void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d
 /* Runner-utils calls (= kernel launches) one forward issues. */
 HOM_EXPORT int32_t homBertLaunchesPerForward(void *program);
 
+/* ---- LLVM-free loader for model libraries compiled by Hands-on-MLIR --------------------
+ * The calling protocol of the reference's ExecutionEngine
+ * (include/ExecutionEngine/ExecutionEngine.h:114-166, lib/ExecutionEngine/ExecutionEngine.cpp:44-97)
+ * with dlopen/dlsym only: `_hom_ciface_<fn>_argNum`, `_hom_ciface_<fn>_initFn` (run once, their
+ * tensors cached) and `_hom_ciface_<fn>` with the `void **` packing of
+ * lib/Conversions/Function/UnifyLLVMFuncInterface.cpp:74-122.
+ * `user_slots[i]` points at the i-th scalar argument of <fn> (an unranked memref contributes
+ * two slots, &rank and &descriptor); `result_storage` points at storage for the result (a
+ * HomUnrankedMemRef for a model returning one tensor).  homModelInvoke returns the runner-utils
+ * error code after the call (0 = ok). */
+HOM_EXPORT void *homModelOpen(const char *so_path);
+HOM_EXPORT int homModelInvoke(void *model, const char *fn, int32_t n_user_slots, void **user_slots,
+                              void *result_storage);
+HOM_EXPORT int32_t homModelInitTensorCount(void *model, const char *fn);
+HOM_EXPORT const char *homModelLastError(void *model);
+HOM_EXPORT void homModelClose(void *model);
+
 #ifdef __cplusplus
 }
 #endif

@@ -162,3 +162,28 @@ def test_flop_model_matches_the_survey_figures(pkg):
     assert len(base.weight_names()) == 3 + 4 * 12
     assert base.weight_shape("w1_3", 128) == (1, 768, 3072)
     assert base.weight_shape("w1_3", 128, nk=True) == (1, 3072, 768)
+
+
+def test_model_loader_protocol_on_cpu(pkg, hom, tmp_path):
+    """The LLVM-free loader against a stub model library that touches no GPU: argNum and initFn
+    run once, hoisted tensors come first, user arguments keep their slots, the result comes
+    back through the last slot."""
+    import subprocess
+    from hands_on_mlir_b200.bert_program import ModelLibrary
+    so = tmp_path / "libecho.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-O1", "-o", str(so),
+                    str(REPO / "tests" / "model_stub" / "cpu_echo_model.c")], check=True)
+    model = ModelLibrary(so)
+    assert model.init_tensor_count("forward") == -1  # nothing cached before the first call
+    x = pkg.MemRef(0xABC0, (4, 8))
+    for call in range(2):
+        res = model.invoke("forward", [x, ctypes.c_int32(7 + call)])
+        rec = ctypes.cast(res.descriptor, ctypes.POINTER(ctypes.c_int64))
+        assert res.rank == 2
+        assert [rec[i] for i in range(6)] == [1, 1000, 2, 1001, 3, 1002]
+        assert rec[6] == 2 and rec[7] == 0xABC0 and rec[8] == 7 + call
+        assert rec[9] == 1  # initFn ran exactly once
+    assert model.init_tensor_count("forward") == 3
+    with pytest.raises(pkg.HomError):
+        model.invoke("no_such_function", [])
+    model.close()

@@ -130,3 +130,40 @@ def test_nk_weight_layout_path(hom, cuda, oracle):
     want = oracle.bert_encoder(w, ids, mask, types, heads=cfg.heads, eps=cfg.eps)
     assert_end_to_end_close(got, want, "[N,K] weights")
     prog.close()
+
+
+def test_loader_runs_a_model_library_against_the_runner(hom, cuda, oracle, tmp_path):
+    """forward(x) = layernorm(x . W) as a model library with the compiler's `_hom_ciface_*`
+    wrappers, loaded through the LLVM-free loader and linked against the runner library."""
+    import subprocess
+    from pathlib import Path
+    from hands_on_mlir_b200.bert_program import ModelLibrary
+    from hands_on_mlir_b200 import MemRef, RUNNER_LIB
+    repo = Path(__file__).resolve().parents[1]
+    so = tmp_path / "liblinear_ln.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-O1", f"-I{repo / 'include'}", "-o", str(so),
+                    str(repo / "tests" / "model_stub" / "linear_ln_model.c"),
+                    f"-L{RUNNER_LIB.parent}", "-lhands_on_mlir_nvgpu_runner_utils",
+                    f"-Wl,-rpath,{RUNNER_LIB.parent}"], check=True)
+    rng = np.random.Generator(np.random.PCG64(11))
+    W = f16(rng.normal(0, 0.1, (1, 64, 96)))
+    X = f16(rng.normal(0, 1, (2, 128, 64)))
+    with open(tmp_path / "0.txt", "w") as f:
+        f.write("1 64 96\n" + " ".join(repr(float(v)) for v in W.astype(np.float32).ravel()) + "\n")
+    hom.lib.homSetConstantDir(str(tmp_path).encode())
+    model = ModelLibrary(so)
+    tx = to_dev(X, cuda)
+    for _ in range(2):
+        res = model.invoke("forward", [MemRef.of(tx)])
+    assert model.init_tensor_count("forward") == 2
+    out = MemRef.from_unranked(res)
+    assert out.shape == [2, 128, 96]
+    import torch
+    got = torch.empty((2, 128, 96), dtype=torch.float16, device=cuda)
+    rows = torch.arange(256, dtype=torch.int64, device=cuda).reshape(2, 128)
+    hom.gather("F16", rows, MemRef(out.data_ptr, (1, 256, 96)), got)
+    hom.synchronize()
+    want = oracle.layernorm_f16(oracle.gemm_f16(X, W), 1e-12)
+    from util import assert_close_f16
+    assert_close_f16(got.cpu().numpy(), want, "model library forward", rtol=2e-3, atol=2e-3)
+    model.close()

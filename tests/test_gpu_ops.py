@@ -92,6 +92,31 @@ def test_nvte_gemm_transb(hom, cuda, oracle, shape, act, beta, tile):
                      f"nvte {shape} act {act} beta {beta}")
 
 
+@pytest.mark.parametrize("shape,act,beta", [((1, 128, 100, 64), 0, 0.0), ((2, 100, 30, 72), 1, 0.0),
+                                            ((1, 64, 31, 64), 0, 1.0), ((3, 130, 1001, 136), 0, 1.0),
+                                            ((1, 256, 30522, 768), 0, 0.0)])
+def test_nvte_gemm_n_not_multiple_of_8(hom, cuda, oracle, shape, act, beta):
+    """B as [1,N,K] with N % 8 != 0 (the MLM decoder, vocab 30522, examples/torch/bert/bert.cu:25,140):
+    rows of C / D are not 16-byte aligned, so the epilogue reads and writes them without TMA."""
+    bs, m, n, k = shape
+    rng = _rng(13)
+    A = rng.uniform(-1, 1, (bs, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.03, (1, n, k)).astype(np.float16)
+    C = rng.normal(0, 1, (bs, m, n)).astype(np.float16) if beta else None
+    got = _run_gemm(hom, cuda, A, B, C, nk=True, act=act, beta=beta, alias=bool(beta))
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, b_is_nk=True, act=act, beta=beta), f"nvte odd N {shape}")
+
+
+def test_cutlass_layout_rejects_n_not_multiple_of_8(hom, cuda, pkg):
+    import torch
+    A = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
+    B = torch.zeros((1, 64, 100), dtype=torch.float16, device=cuda)
+    D = torch.zeros((1, 128, 100), dtype=torch.float16, device=cuda)
+    with pytest.raises(pkg.HomError) as e:
+        hom.cutlassGemmF16(A, B, D, D)
+    assert e.value.code == 2
+
+
 def test_gemm_constant_inputs_like_reference_harness(hom, cuda):
     """A = 0.1, B = 0.2, 512x768x768: every output is K * 0.02 within 1e-1
     (the check of examples/torch/linear/cuda/b.cu:17-66)."""
