@@ -95,6 +95,10 @@ def _replay_lib():
                                        c_void_p, ctypes.POINTER(UnrankedMemRef), c_int]
         lib.homBertForwardHost.restype = c_int
         lib.homBertForwardHost.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int]
+        lib.homBertForwardHostAsync.restype = c_int
+        lib.homBertForwardHostAsync.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int]
+        lib.homBertWaitHost.restype = c_int
+        lib.homBertWaitHost.argtypes = [c_void_p]
         lib.homBertHostTraffic.argtypes = [c_void_p, ctypes.POINTER(c_int64),
                                            ctypes.POINTER(c_int64)]
         lib.homBertLaunchesPerForward.restype = c_int32
@@ -164,6 +168,18 @@ class BertProgram:
             return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
         self._rc(self._lib.homBertForwardHost(self._handle, ptr(ids), ptr(mask), ptr(types),
                                               ptr(out), int(use_graph)))
+
+    def forward_host_async(self, ids, mask, types, out, use_graph: bool = False):
+        """Like forward_host but returns once the step is enqueued; `out` is filled by a copy
+        stream while later steps run.  Alternate between two `out` buffers; call wait_host()
+        before reading them."""
+        def ptr(x):
+            return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
+        self._rc(self._lib.homBertForwardHostAsync(self._handle, ptr(ids), ptr(mask), ptr(types),
+                                                   ptr(out), int(use_graph)))
+
+    def wait_host(self):
+        self._rc(self._lib.homBertWaitHost(self._handle))
 
     def host_traffic(self) -> tuple[int, int]:
         a, b = c_int64(), c_int64()

@@ -57,6 +57,13 @@ struct Program {
   Tensor ids_dev, mask_dev, types_dev;     // staging for the host entry point
   cudaStream_t own_stream = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
+  // pipelined host entry point: two device result slots, a copy stream and hand-off events
+  Tensor result_slot[2];
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t slot_ready[2] = {nullptr, nullptr};  // result copied into the slot (compute stream)
+  cudaEvent_t slot_done[2] = {nullptr, nullptr};   // slot delivered to the host (copy stream)
+  bool slot_busy[2] = {false, false};
+  unsigned long long host_steps = 0;
   void *graph_ids = nullptr, *graph_mask = nullptr, *graph_types = nullptr;
   bool warmed_up = false;
 };
@@ -207,6 +214,15 @@ void homBertDestroy(void *program) {
   if (!p) return;
   if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
   if (p->own_stream) cudaStreamDestroy(p->own_stream);
+  if (p->copy_stream) {
+    cudaStreamSynchronize(p->copy_stream);
+    cudaStreamDestroy(p->copy_stream);
+  }
+  for (int i = 0; i < 2; ++i) {
+    if (p->slot_ready[i]) cudaEventDestroy(p->slot_ready[i]);
+    if (p->slot_done[i]) cudaEventDestroy(p->slot_done[i]);
+    release(p->result_slot[i], true);
+  }
   for (Tensor &w : p->weights) release(w, true);
   release(p->x, true);
   release(p->type_rows, true);
@@ -282,6 +298,57 @@ int homBertForwardHost(void *program, const int64_t *ids_host, const int64_t *ma
   const size_t out_bytes = static_cast<size_t>(p->cfg.batch) * p->cfg.seq * p->cfg.hidden * 2;
   if (cudaMemcpyAsync(out_host, p->x.data(), out_bytes, cudaMemcpyDeviceToHost, stream) != cudaSuccess)
     return HOM_ERR_CUDA;
+  return homSynchronize();
+}
+
+int homBertForwardHostAsync(void *program, const int64_t *ids_host, const int64_t *mask_host,
+                            const int64_t *types_host, void *out_host, int use_graph) {
+  auto *p = static_cast<Program *>(program);
+  if (!p || !ids_host || !mask_host || !types_host || !out_host) return HOM_ERR_INVALID;
+  const HomBertConfig &c = p->cfg;
+  if (!p->copy_stream) {
+    if (cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking) != cudaSuccess) return HOM_ERR_CUDA;
+    for (int i = 0; i < 2; ++i) {
+      p->result_slot[i] = from_alloc(alloc3DMemRefNVGPUF16(c.batch, c.seq, c.hidden));
+      if (!p->result_slot[i].data() ||
+          cudaEventCreateWithFlags(&p->slot_ready[i], cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&p->slot_done[i], cudaEventDisableTiming) != cudaSuccess)
+        return HOM_ERR_CUDA;
+    }
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(homGetStream());
+  const int slot = static_cast<int>(p->host_steps & 1);
+  // The slot's previous delivery must be over before its device buffer is overwritten.
+  if (p->slot_busy[slot] && cudaStreamWaitEvent(stream, p->slot_done[slot], 0) != cudaSuccess)
+    return HOM_ERR_CUDA;
+  const size_t plane = static_cast<size_t>(c.batch) * c.seq * 8;
+  if (cudaMemcpyAsync(p->ids_dev.data(), ids_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(p->mask_dev.data(), mask_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(p->types_dev.data(), types_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+    return HOM_ERR_CUDA;
+  const int rc = forward_impl(*p, 2, p->ids_dev.desc, 2, p->mask_dev.desc, 2, p->types_dev.desc, use_graph);
+  if (rc != 0) return rc;
+  const size_t out_bytes = static_cast<size_t>(c.batch) * c.seq * c.hidden * 2;
+  // The hidden-state buffer is reused by the next forward: park the result in the slot, then
+  // let the copy stream deliver it while the next forward runs.
+  if (cudaMemcpyAsync(p->result_slot[slot].data(), p->x.data(), out_bytes, cudaMemcpyDeviceToDevice,
+                      stream) != cudaSuccess ||
+      cudaEventRecord(p->slot_ready[slot], stream) != cudaSuccess ||
+      cudaStreamWaitEvent(p->copy_stream, p->slot_ready[slot], 0) != cudaSuccess ||
+      cudaMemcpyAsync(out_host, p->result_slot[slot].data(), out_bytes, cudaMemcpyDeviceToHost,
+                      p->copy_stream) != cudaSuccess ||
+      cudaEventRecord(p->slot_done[slot], p->copy_stream) != cudaSuccess)
+    return HOM_ERR_CUDA;
+  p->slot_busy[slot] = true;
+  ++p->host_steps;
+  return 0;
+}
+
+int homBertWaitHost(void *program) {
+  auto *p = static_cast<Program *>(program);
+  if (!p) return HOM_ERR_INVALID;
+  if (p->copy_stream && cudaStreamSynchronize(p->copy_stream) != cudaSuccess) return HOM_ERR_CUDA;
+  p->slot_busy[0] = p->slot_busy[1] = false;
   return homSynchronize();
 }
 

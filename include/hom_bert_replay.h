@@ -72,6 +72,15 @@ HOM_EXPORT int homBertForward(void *program, int64_t rankIds, void *ids, int64_t
 HOM_EXPORT int homBertForwardHost(void *program, const int64_t *ids_host, const int64_t *mask_host,
                                   const int64_t *types_host, void *out_host, int use_graph);
 
+/* The same step without the final wait: the result is parked in one of two device slots and
+ * delivered to out_host by a copy stream while the caller already issues the next step.
+ * At most two steps are in flight; out_host buffers of consecutive calls must differ.
+ * homBertWaitHost() waits until every issued step has been delivered. */
+HOM_EXPORT int homBertForwardHostAsync(void *program, const int64_t *ids_host,
+                                       const int64_t *mask_host, const int64_t *types_host,
+                                       void *out_host, int use_graph);
+HOM_EXPORT int homBertWaitHost(void *program);
+
 /* Bytes moved per homBertForwardHost call (host->device, device->host). */
 HOM_EXPORT void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d2h_bytes);
 /* Runner-utils calls (= kernel launches) one forward issues. */

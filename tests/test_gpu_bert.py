@@ -82,6 +82,14 @@ def test_graph_replay_and_host_entry_point_are_bit_identical(hom, cuda, oracle):
         out_h.zero_()
         prog.forward_host(hi, hm, ht, out_h, use_graph=use_graph)
         assert_bits_equal(out_h.numpy(), eager, f"host entry point (graph={use_graph})")
+    # pipelined variant: alternate two host buffers, results complete after wait_host()
+    out_h2 = torch.empty_like(out_h).pin_memory()
+    for i in range(5):
+        (out_h, out_h2)[i & 1].zero_()
+        prog.forward_host_async(hi, hm, ht, (out_h, out_h2)[i & 1], use_graph=True)
+    prog.wait_host()
+    assert_bits_equal(out_h.numpy(), eager, "async host entry point, slot 0")
+    assert_bits_equal(out_h2.numpy(), eager, "async host entry point, slot 1")
     h2d, d2h = prog.host_traffic()
     assert h2d == 3 * B * S * 8 and d2h == B * S * cfg.hidden * 2
     prog.close()
