@@ -11,6 +11,8 @@
 // Replaces the reference's cuDNN fused attention behind TransformerEngine
 // (include/NVGPUKernels/BertAttentionRunner.h:52-136: layout BS3HD, no bias, padding mask,
 // no dropout, inference).
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -43,7 +45,15 @@ struct Params {
   int seq, heads;
   float scale_log2;  // softmax scale * log2(e)
   int *status;
+  long long *prof;  // phase stamps of two CTAs (diagnostic, HOM_ATTN_PROFILE), else null
+  int timeline_slot;  // >= 0: record first/last CTA entry and exit times instead (HOM_ATTN_TIMELINE)
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
 attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) {
@@ -288,9 +298,21 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
 // TMA store through a 3-D [hidden, seq, batch] view of the output (rows beyond seq are
 // clipped).  48 KB of shared memory and 128 tensor-memory columns per CTA let four CTAs share
 // an SM, which is what hides the load -> MMA -> softmax -> MMA -> store latency chain.
-constexpr uint32_t kSmemBytes1 = 3 * kTileBytes + 64 + 1024;
+constexpr int kThreads1 = 256;  // two threads per query row
+constexpr uint32_t kXchgBytes = 2 * 2 * kTile * 4;  // row maxima and row sums of both halves
+constexpr uint32_t kSmemBytes1 = 3 * kTileBytes + 64 + kXchgBytes + 1024;
 
-__global__ void __launch_bounds__(kThreads, 4)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// A query row is shared by threads `row` and `row + 128`: each owns 64 of the 128 key
+// columns (one 128-byte P sub-tile row) and 32 of the 64 output columns.  Only the 32-column
+// chunks that hold valid keys are read, the chunk that holds the boundary is masked, and the
+// P.V product stops at the last 16-key group with a valid key.
+__global__ void __launch_bounds__(kThreads1, 4)
 attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
                                  const __grid_constant__ CUtensorMap tmOut, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -299,10 +321,35 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
   pdl_launch_dependents();
+  const long long t_entry = clock64();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int row = tid & (kTile - 1);
+  const int hf = tid >> 7;  // which half of the key columns / output columns
   const int head = blockIdx.y, batch = blockIdx.z;
   const int hidden = p.heads * kHeadDim;
+  long long *stamps = nullptr;
+  if (p.prof != nullptr && tid == 0 && p.timeline_slot >= 0) {
+    const long long now = static_cast<long long>(global_ns());
+    atomicMin(p.prof + 32 + 4 * p.timeline_slot, now);
+    atomicMax(p.prof + 33 + 4 * p.timeline_slot, now);
+  } else if (p.prof != nullptr && tid == 0) {
+    if (blockIdx.y == 0 && blockIdx.z == 0) stamps = p.prof;
+    else if (blockIdx.y == gridDim.y / 2 && blockIdx.z == gridDim.z / 2) stamps = p.prof + 16;
+  }
+  // per-CTA wall-clock stamps of timeline launches 0 and 5: {entry, loaded, P written, exit}
+  long long *cta_ns = nullptr;
+  if (p.prof != nullptr && tid == 0 && (p.timeline_slot == 0 || p.timeline_slot == 5)) {
+    const int cta = blockIdx.z * gridDim.y + blockIdx.y;
+    if (cta < 448) cta_ns = p.prof + 64 + (p.timeline_slot == 5 ? 2016 : 0) + 4 * cta;
+    if (cta_ns) cta_ns[0] = static_cast<long long>(global_ns());
+  }
+  auto stamp = [&](int slot) {
+    if (stamps) stamps[slot] = clock64() - t_entry;
+    if (cta_ns && slot == 3) cta_ns[1] = static_cast<long long>(global_ns());
+    if (cta_ns && slot == 6) cta_ns[2] = static_cast<long long>(global_ns());
+    if (cta_ns && slot == 9) cta_ns[3] = static_cast<long long>(global_ns());
+  };
 
   const uint32_t smem_q = smem_base, smem_k = smem_base + kTileBytes, smem_v = smem_base + 2 * kTileBytes;
   const uint32_t smem_p = smem_base;  // two 128 x 64 sub-tiles over Q|K
@@ -310,6 +357,8 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   const uint32_t bar_s = bar_load + 8, bar_o = bar_load + 16;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + 3 * kTileBytes + 24);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float *xchg_max = reinterpret_cast<float *>(smem_gen + 3 * kTileBytes + 64);  // [2][128]
+  float *xchg_sum = xchg_max + 2 * kTile;                                       // [2][128]
 
   if (tid == 0) {
     mbar_init(bar_load, 1);
@@ -328,22 +377,29 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_acc = *tmem_slot;
-  const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  stamp(0);
 
   pdl_wait();  // cu_seqlens and the packed QKV come from earlier kernels of the stream
+  stamp(1);
+  // The tiles do not depend on the valid length: request them before reading it.
+  if (tid == 0) {
+    const int row_base = batch * p.seq;
+    mbar_arrive_expect_tx(bar_load, 3 * kTileBytes);
+    tma_load_2d(smem_q, &tmQKV, bar_load, head * kHeadDim, row_base);
+    tma_load_2d(smem_k, &tmQKV, bar_load, hidden + head * kHeadDim, row_base);
+    tma_load_2d(smem_v, &tmQKV, bar_load, 2 * hidden + head * kHeadDim, row_base);
+  }
   int len = p.cu_seqlens[batch + 1] - p.cu_seqlens[batch];
   len = max(0, min(len, p.seq));
+  stamp(2);
 
   bool ok = true;
   float inv = 0.f;
   if (len > 0) {
     if (tid == 0) {
-      const int row_base = batch * p.seq;
-      mbar_arrive_expect_tx(bar_load, 3 * kTileBytes);
-      tma_load_2d(smem_q, &tmQKV, bar_load, head * kHeadDim, row_base);
-      tma_load_2d(smem_k, &tmQKV, bar_load, hidden + head * kHeadDim, row_base);
-      tma_load_2d(smem_v, &tmQKV, bar_load, 2 * hidden + head * kHeadDim, row_base);
       if (mbar_wait(bar_load, 0, abort_flag, p.status, kDevWaitTimeoutAttention)) {
+        stamp(3);
         tc_fence_after_sync();
         constexpr uint32_t idesc_s = make_idesc_f16(kTile, kTile, false, false);
 #pragma unroll
@@ -357,56 +413,91 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
     }
     ok = mbar_wait(bar_s, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
     ok = __syncthreads_and(ok);
+    stamp(4);
     if (ok) {
       tc_fence_after_sync();
-      // softmax over the valid keys: one query row per thread
-      float m_row = -INFINITY;
+      const bool row_live = row < len;  // padded query rows are written as zeros
+      // tcgen05.ld is warp-collective: the whole warp takes part as soon as one of its rows is
+      // live; what its padded rows compute is never used.
+      const bool warp_live = (warp & 3) * 32 < len;
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      // pass 1: maximum of this thread's scaled scores over the valid keys
+      float m_part = -INFINITY;
+      if (warp_live) {
 #pragma unroll 1
-      for (int c = 0; c < kTile / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 2 * hf; c < 2 * hf + 2 && c * 32 < len; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
+          tmem_ld_wait();
+          if ((c + 1) * 32 <= len) {
+            float m0 = m_part, m1 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < len) m_row = fmaxf(m_row, __uint_as_float(r[i]) * p.scale_log2);
-      }
-      float l_row = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kTile / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
-        tmem_ld_wait();
-        const uint32_t sub = smem_p + (c >> 1) * kTileBytes + tid * 128;
+            for (int i = 0; i < 32; i += 2) {
+              const float2 x = __fmul2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2);
+              m0 = fmaxf(m0, x.x);
+              m1 = fmaxf(m1, x.y);
+            }
+            m_part = fmaxf(m0, m1);
+          } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t w[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int i0 = g * 8 + 2 * j;
-            float e0 = exp2f(fmaf(__uint_as_float(r[i0]), p.scale_log2, -m_row));
-            float e1 = exp2f(fmaf(__uint_as_float(r[i0 + 1]), p.scale_log2, -m_row));
-            e0 = (c * 32 + i0 < len) ? e0 : 0.f;
-            e1 = (c * 32 + i0 + 1 < len) ? e1 : 0.f;
-            l_row += e0 + e1;
-            const __half2 h = __floats2half2_rn(e0, e1);
-            w[j] = *reinterpret_cast<const uint32_t *>(&h);
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < len) m_part = fmaxf(m_part, __uint_as_float(r[i]) * p.scale_log2);
           }
-          const uint32_t chunk = (c & 1) * 4 + g;
-          const uint32_t addr = sub + ((chunk ^ (tid & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
-                       "r"(w[2]), "r"(w[3])
-                       : "memory");
         }
       }
-      inv = (tid < len && l_row > 0.f) ? 1.f / l_row : 0.f;
+      xchg_max[hf * kTile + row] = m_part;
+      __syncthreads();
+      stamp(5);
+      const float m_row = fmaxf(m_part, xchg_max[(hf ^ 1) * kTile + row]);
+      // pass 2: P = exp2(s * scale - m) as fp16 into this thread's sub-tile row, and its sum
+      float2 l2 = make_float2(0.f, 0.f);
+      if (warp_live) {
+        const float2 neg_m2 = make_float2(-m_row, -m_row);
+        const uint32_t sub = smem_p + hf * kTileBytes + row * 128;
+#pragma unroll 1
+        for (int c = 2 * hf; c < 2 * hf + 2 && c * 32 < len; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
+          tmem_ld_wait();
+          const bool full = (c + 1) * 32 <= len;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i0 = g * 8 + 2 * j;
+              const float2 x = __ffma2_rn(
+                  make_float2(__uint_as_float(r[i0]), __uint_as_float(r[i0 + 1])), scale2, neg_m2);
+              float2 e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+              if (!full) {
+                e.x = (c * 32 + i0 < len) ? e.x : 0.f;
+                e.y = (c * 32 + i0 + 1 < len) ? e.y : 0.f;
+              }
+              l2 = __fadd2_rn(l2, e);
+              const __half2 h = __floats2half2_rn(e.x, e.y);
+              w[j] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            const uint32_t chunk = (c & 1) * 4 + g;
+            const uint32_t addr = sub + ((chunk ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                         "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
+        }
+      }
+      const float l_part = l2.x + l2.y;
+      xchg_sum[hf * kTile + row] = l_part;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncthreads();  // P complete, and every thread is done reading S
+      stamp(6);
+      const float l_row = l_part + xchg_sum[(hf ^ 1) * kTile + row];
+      inv = (row_live && l_row > 0.f) ? 1.f / l_row : 0.f;
       if (tid == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc_o = make_idesc_f16(kTile, kHeadDim, false, true);
-#pragma unroll
-        for (int k = 0; k < kTile / 16; ++k) {
+        const int k_steps = (len + 15) >> 4;  // key groups beyond the last valid key hold no P
+        for (int k = 0; k < k_steps; ++k) {
           const uint64_t da =
               make_smem_desc_sw128(smem_p + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_v + k * 2048, kTileBytes, 1024);
@@ -416,40 +507,49 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
       }
       ok = mbar_wait(bar_o, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
       ok = __syncthreads_and(ok);
+      stamp(7);
     }
   }
 
+  if (len == 0) {
+    // Nothing was computed, but the tile copies are in flight: they must land before the
+    // zero tile is staged over V (and before shared memory is released).
+    ok = mbar_wait(bar_load, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
+    ok = __syncthreads_and(ok);
+  }
   if (ok) {
     if (len > 0) tc_fence_after_sync();
-    // O (or zeros for padded rows / empty sequences) -> swizzled staging over the V tile
-    const uint32_t my_row = smem_v + tid * 128;
+    // O (or zeros for padded rows / empty sequences) -> swizzled staging over the V tile;
+    // this thread owns output columns [32 * hf, +32) of its row.
+    const uint32_t my_row = smem_v + row * 128;
+    uint32_t r[32];
+    if (len > 0) {  // block-uniform: the load is warp-collective
+      tmem_ld_32x32(tmem_acc + lane_sel + hf * 32, r);
+      tmem_ld_wait();
+    }
+    const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-    for (int c = 0; c < kHeadDim / 32; ++c) {
-      uint32_t r[32];
-      if (len > 0) {
-        tmem_ld_32x32(tmem_acc + lane_sel + c * 32, r);
-        tmem_ld_wait();
-      }
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint32_t w[4];
+    for (int g = 0; g < 4; ++g) {
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+      if (inv != 0.f) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a = len > 0 ? __uint_as_float(r[g * 8 + 2 * j]) * inv : 0.f;
-          const float b = len > 0 ? __uint_as_float(r[g * 8 + 2 * j + 1]) * inv : 0.f;
-          const __half2 h = (inv != 0.f) ? __floats2half2_rn(a, b) : __floats2half2_rn(0.f, 0.f);
+          const float2 o = __fmul2_rn(make_float2(__uint_as_float(r[g * 8 + 2 * j]),
+                                                  __uint_as_float(r[g * 8 + 2 * j + 1])), inv2);
+          const __half2 h = __floats2half2_rn(o.x, o.y);
           w[j] = *reinterpret_cast<const uint32_t *>(&h);
         }
-        const uint32_t chunk = c * 4 + g;
-        const uint32_t addr = my_row + ((chunk ^ (tid & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
-                     "r"(w[2]), "r"(w[3])
-                     : "memory");
       }
+      const uint32_t chunk = hf * 4 + g;
+      const uint32_t addr = my_row + ((chunk ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                   "r"(w[2]), "r"(w[3])
+                   : "memory");
     }
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
+    stamp(8);
     if (tid == 0) {
       asm volatile(
           "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
@@ -459,6 +559,7 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
           : "memory");
       bulk_commit_group();
       bulk_wait_group_read_0();
+      stamp(9);
     }
   } else if (tid == 0) {
     // Let copies that are still in flight land before the shared memory is released.
@@ -472,6 +573,11 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_acc, 128);
+  }
+  if (p.prof != nullptr && tid == 0 && p.timeline_slot >= 0) {
+    const long long now = static_cast<long long>(global_ns());
+    atomicMin(p.prof + 34 + 4 * p.timeline_slot, now);
+    atomicMax(p.prof + 35 + 4 * p.timeline_slot, now);
   }
 }
 
@@ -548,6 +654,18 @@ bool run(const Problem &pb, cudaStream_t stream) {
   p.heads = static_cast<int>(pb.heads);
   p.scale_log2 = pb.scale * 1.44269504088896340736f;
   p.status = device_status_word();
+  static const bool want_prof = std::getenv("HOM_ATTN_PROFILE") != nullptr;
+  p.prof = nullptr;
+  p.timeline_slot = -1;
+  if (want_prof) {
+    static int timeline_calls = 0;
+    if (std::getenv("HOM_ATTN_TIMELINE")) {
+      p.prof = gemm::profile_buffer_raw();
+      p.timeline_slot = timeline_calls++ & 7;
+    } else {
+      p.prof = gemm::profile_buffer();
+    }
+  }
   dim3 grid(static_cast<unsigned>((pb.seq + kTile - 1) / kTile), static_cast<unsigned>(pb.heads),
             static_cast<unsigned>(pb.bs));
   const double d = kHeadDim;
@@ -565,9 +683,21 @@ bool run(const Problem &pb, cudaStream_t stream) {
     }
     CUtensorMap tm_out;
     if (!make_out_map(pb.out, pb.heads * kHeadDim, pb.seq, pb.bs, &tm_out)) return false;
-    return check_cuda(launch_pdl(attention_f16_single_tile_kernel, grid, dim3(kThreads), kSmemBytes1,
-                                 stream, 1, tm, tm_out, p),
-                      "attention kernel launch");
+    const bool launched = check_cuda(launch_pdl(attention_f16_single_tile_kernel, grid, dim3(kThreads1),
+                                                kSmemBytes1, stream, 1, tm, tm_out, p),
+                                     "attention kernel launch");
+    if (p.prof && p.timeline_slot < 0) {
+      long long h[32];
+      cudaStreamSynchronize(stream);
+      cudaMemcpy(h, p.prof, sizeof(h), cudaMemcpyDeviceToHost);
+      for (int c = 0; c < 2; ++c)
+        fprintf(stderr,
+                "[hom] attention CTA %s: setup %lld | dependency %lld | len %lld | loaded %lld | S %lld | "
+                "max %lld | P %lld | O %lld | staged %lld | stored %lld cycles\n",
+                c ? "mid" : "0", h[16 * c], h[16 * c + 1], h[16 * c + 2], h[16 * c + 3], h[16 * c + 4],
+                h[16 * c + 5], h[16 * c + 6], h[16 * c + 7], h[16 * c + 8], h[16 * c + 9]);
+    }
+    return launched;
   }
   return check_cuda(launch_pdl(attention_f16_kernel, grid, dim3(kThreads), kSmemBytes, stream, 1, tm, p),
                     "attention kernel launch");

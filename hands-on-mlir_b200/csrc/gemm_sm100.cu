@@ -359,14 +359,22 @@ long long *profile_buffer() {
   static bool checked = false;
   if (!checked) {
     checked = true;
-    if (std::getenv("HOM_GEMM_PROFILE")) {
-      if (cudaMalloc(&g_profile_buf, 64 * sizeof(long long)) != cudaSuccess) g_profile_buf = nullptr;
-      else cudaMemset(g_profile_buf, 0, 64 * sizeof(long long));
+    if (std::getenv("HOM_GEMM_PROFILE") || std::getenv("HOM_ATTN_PROFILE")) {
+      if (cudaMalloc(&g_profile_buf, 4096 * sizeof(long long)) != cudaSuccess) g_profile_buf = nullptr;
+      else {
+        cudaMemset(g_profile_buf, 0, 4096 * sizeof(long long));
+        // slots [32, 64): {first entry, last entry, first exit, last exit} of eight launches
+        long long init[32];
+        for (int i = 0; i < 32; ++i) init[i] = (i & 1) == 0 ? 0x7fffffffffffffffLL : 0;
+        cudaMemcpy(g_profile_buf + 32, init, sizeof(init), cudaMemcpyHostToDevice);
+      }
     }
   }
   if (g_profile_buf && !std::getenv("HOM_GEMM_TIMELINE")) cudaMemset(g_profile_buf, 0, 15 * sizeof(long long));
   return g_profile_buf;
 }
+
+long long *profile_buffer_raw() { return g_profile_buf; }
 
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream) {
   if (std::getenv("HOM_GEMM_TIMELINE")) return;  // stamps are read back by the caller

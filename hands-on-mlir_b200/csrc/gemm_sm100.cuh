@@ -41,6 +41,7 @@ int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, i
 
 // Diagnostics, enabled by HOM_GEMM_PROFILE=1 only: per-role cycle counters of CTA 0.
 long long *profile_buffer();
+long long *profile_buffer_raw();  // the buffer if it exists; touches nothing
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream);
 
 // Cached cuTensorMapEncodeTiled for a 2-D fp16 tensor [outer, inner], 128-byte swizzle.

@@ -693,6 +693,12 @@ __attribute__((visibility("default"))) void homDebugReadGemmProfile(long long *o
   if (buf) cudaMemcpy(out, buf, 64 * sizeof(long long), cudaMemcpyDeviceToHost);
 }
 
+__attribute__((visibility("default"))) void homDebugReadProfile(long long *out, int count) {
+  long long *buf = hom::gemm::profile_buffer_raw();
+  cudaDeviceSynchronize();
+  if (buf && count > 0 && count <= 4096) cudaMemcpy(out, buf, count * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+
 void homSetConstantDir(const char *dir) {
   std::lock_guard<std::mutex> lock(g_dir_mutex);
   g_constant_dir = dir ? dir : "";
