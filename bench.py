@@ -52,6 +52,26 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (read + written) per launch from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum); keyed by the --op case, "bert-base" is the mean
+# over the 48 GEMM launches of one step with caches as the preceding kernels leave them.
+NCU_TRAFFIC_BYTES = {
+    "bert-base": {"bytes": 11.05e6, "source": "profiles/launch_list_bert_base_b32_s128.txt"},
+    "gemm-ffn1": {"bytes": 11.06e6, "source": "profiles/gemm_pair_256x256_bert_base_ffn1.txt"},
+    "gemm-qkv": {"bytes": 9.88e6, "source": "profiles/gemm_pair_256x256_bert_base_qkv.txt"},
+    "gemm-ffn2": {"bytes": 36.22e6, "source": "profiles/gemm_1cta_128x192_bert_base_ffn2.txt"},
+    "gemm-large-ffn1": {"bytes": 122.4e6, "source": "profiles/gemm_pair_256x256_bert_large_ffn1_m16384.txt"},
+    "ln-c2": {"bytes": 12.60e6, "source": "profiles/layernorm_residual_affine_4096x768.txt"},
+    "ln-large": {"bytes": 477.6e6, "source": "profiles/layernorm_inplace_131072x1024.txt"},
+    "attn-c3": {"bytes": 18.90e6, "source": "profiles/attention_single_tile_bs32_seq128_h12.txt"},
+}
+
+
+def ncu_traffic(key):
+    t = NCU_TRAFFIC_BYTES.get(key)
+    return (t["bytes"], t["source"]) if t else (None, None)
+
+
 def load_peaks():
     p = REPO / "MEASURED_PEAKS.json"
     if p.exists():
@@ -369,7 +389,8 @@ def run_op_arm(args):
                           f"{len(sets)} rotating buffer sets, {len(sets) * per_set / 1e6:.0f} MB > 126 MB L2")},
         "gpu_launches": args.steps,
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                     "frac": achieved / peak, "peak_source": peak_note, "traffic": None,
+                     "frac": achieved / peak, "peak_source": peak_note,
+                     "traffic": ncu_traffic(args.op)[0], "traffic_source": ncu_traffic(args.op)[1],
                      "algorithmic_bytes": nbytes,
                      "algorithmic_flops": flops if kind != "ln" else 0.0},
         "clocks": clocks.summary(),
@@ -517,7 +538,9 @@ def run_gpu_arm(args, cfg, workload):
         "bound": "tensor", "kernel": "gemm_f16_kernel (all GEMM launches of a step)",
         "achieved": gemm_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
         "frac": gemm_tflops / tensor_peak, "peak_source": f"{peak_src} (sustained dense bf16/fp16)",
-        "traffic": None,
+        "traffic": ncu_traffic(args.workload)[0],
+        "traffic_source": ncu_traffic(args.workload)[1],
+        "algorithmic_bytes_per_launch": gemm["bytes"] / max(1, gemm["launches"]),
         "launches_per_step": gemm["launches"] // n_prof,
         "avg_launch_us": 1e3 * gemm["ms"] / max(1, gemm["launches"]),
     }
