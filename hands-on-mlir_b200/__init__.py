@@ -143,6 +143,12 @@ _SIGNATURES = {
     "homGemmQueryTile": (c_int32, [c_int64, c_int64, c_int64, c_int64,
                                    ctypes.POINTER(c_int32), ctypes.POINTER(c_int32),
                                    ctypes.POINTER(c_int32)]),
+    "homGemmTune": (c_int32, [c_int64, c_int64, c_int64, c_int64, c_float, c_float, c_int32, c_int32,
+                              ctypes.POINTER(c_int32), ctypes.POINTER(c_int32),
+                              ctypes.POINTER(c_float), ctypes.POINTER(c_float)]),
+    "homSetConstantCache": (None, [ctypes.c_int]),
+    "homGemmTuneSave": (c_int32, [ctypes.c_char_p]),
+    "homGemmTuneLoad": (c_int32, [ctypes.c_char_p]),
 }
 for _op in ("Add", "Sub", "Mul", "Div"):
     for _ty in ("F32", "F16"):
@@ -309,6 +315,24 @@ class RunnerUtils:
         row = self.lib.homGemmQueryTile(m, n, k, activation, ctypes.byref(bn), ctypes.byref(st),
                                         ctypes.byref(sk))
         return {"row": int(row), "bn": bn.value, "stages": st.value, "split_k": sk.value}
+
+    def gemm_tune(self, m, n, k, activation=0, alpha=1.0, beta=0.0, weights_nk=False, iterations=20):
+        """Time the tile-table rows for one shape (GemmProfiler::profile's contract); the winner
+        is remembered for automatic selection.  Returns row, split_k, best_us and the row times."""
+        row, sk, best = c_int32(), c_int32(), c_float()
+        times = (c_float * 6)()
+        rc = self.lib.homGemmTune(m, n, k, activation, alpha, beta, int(weights_nk), iterations,
+                                  ctypes.byref(row), ctypes.byref(sk), ctypes.byref(best), times)
+        if rc != 0:
+            self.check()
+            raise HomError(rc, "homGemmTune failed")
+        return {"row": row.value, "split_k": sk.value, "best_us": best.value, "row_us": list(times)}
+
+    def gemm_tune_save(self, path) -> int:
+        return int(self.lib.homGemmTuneSave(str(path).encode()))
+
+    def gemm_tune_load(self, path) -> int:
+        return int(self.lib.homGemmTuneLoad(str(path).encode()))
 
 
 _runner: RunnerUtils | None = None

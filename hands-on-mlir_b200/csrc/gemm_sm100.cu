@@ -16,6 +16,9 @@
 // (include/NVGPUKernels/GemmRunner.h:119-310, lib/NVGPUKernels/GemmProfiler.cu:143-236) with a
 // small per-shape tile table.
 #include <cstdlib>
+#include <cstdio>
+#include <tuple>
+#include <map>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -669,11 +672,148 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
                     "gemm kernel launch");
 }
 
+// ---- tuned shapes: (M, N, K, activation) -> tile-table row, filled by tune() or a cache file.
+// Takes the place of the reference's GemmProfiler timing cache
+// (include/NVGPUKernels/GemmProfiler.h:39-41).
+namespace {
+using TuneKey = std::tuple<int64_t, int64_t, int64_t, int>;
+std::map<TuneKey, int> g_tuned;
+std::mutex g_tuned_mutex;
+
+void load_env_cache_once() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (const char *path = std::getenv("HOM_TUNE_CACHE")) tune_cache_load(path);
+  });
+}
+
+__global__ void fill_pattern_kernel(__half *p, size_t n, uint32_t seed, float scale) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    uint32_t h = static_cast<uint32_t>(i) * 2654435761u + seed;
+    h ^= h >> 15;
+    h *= 2246822519u;
+    h ^= h >> 13;
+    p[i] = __float2half((static_cast<float>(h & 0xffff) / 32768.f - 1.f) * scale);
+  }
+}
+}  // namespace
+
+int tuned_row(int64_t m, int64_t n, int64_t k, int act) {
+  load_env_cache_once();
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  auto it = g_tuned.find(TuneKey{m, n, k, act});
+  return it == g_tuned.end() ? 0 : it->second;
+}
+
+int tune_cache_load(const char *path) {
+  FILE *f = path ? std::fopen(path, "r") : nullptr;
+  if (!f) return -1;
+  long long m, n, k;
+  int act, row, count = 0;
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  while (std::fscanf(f, "%lld %lld %lld %d %d", &m, &n, &k, &act, &row) == 5) {
+    if (row >= 1 && row <= kNumTileRows) {
+      g_tuned[TuneKey{m, n, k, act}] = row;
+      ++count;
+    }
+  }
+  std::fclose(f);
+  return count;
+}
+
+int tune_cache_save(const char *path) {
+  FILE *f = path ? std::fopen(path, "w") : nullptr;
+  if (!f) return -1;
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  for (const auto &kv : g_tuned)
+    std::fprintf(f, "%lld %lld %lld %d %d\n", static_cast<long long>(std::get<0>(kv.first)),
+                 static_cast<long long>(std::get<1>(kv.first)),
+                 static_cast<long long>(std::get<2>(kv.first)), std::get<3>(kv.first), kv.second);
+  std::fclose(f);
+  return static_cast<int>(g_tuned.size());
+}
+
+// Times every row of the tile table on scratch buffers of the given shape (the contract of
+// GemmProfiler::profile, lib/NVGPUKernels/GemmProfiler.cu:143-236: warm up, then batches of
+// launches between two events on one stream; beta != 0 reads C = D like the reference does).
+bool tune(int64_t m, int64_t n, int64_t k, int act, float alpha, float beta, bool b_is_nk, int iters,
+          int *best_row, float *best_us, float *row_us, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || (!b_is_nk && n % 8 != 0)) {
+    set_error(HOM_ERR_UNSUPPORTED, "homGemmTune: shape %lld x %lld x %lld is not supported",
+              static_cast<long long>(m), static_cast<long long>(n), static_cast<long long>(k));
+    return false;
+  }
+  if (iters < 1) iters = 20;
+  __half *a = nullptr, *b = nullptr, *d = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  auto cleanup = [&]() {
+    cudaFree(a);
+    cudaFree(b);
+    cudaFree(d);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+  };
+  if (cudaMalloc(&a, sizeof(__half) * m * k) != cudaSuccess || cudaMalloc(&b, sizeof(__half) * k * n) != cudaSuccess ||
+      cudaMalloc(&d, sizeof(__half) * m * n) != cudaSuccess || cudaEventCreate(&e0) != cudaSuccess ||
+      cudaEventCreate(&e1) != cudaSuccess) {
+    cleanup();
+    check_cuda(cudaGetLastError(), "homGemmTune allocation");
+    set_error(HOM_ERR_CUDA, "homGemmTune: could not allocate the scratch operands");
+    return false;
+  }
+  fill_pattern_kernel<<<592, 256, 0, stream>>>(a, static_cast<size_t>(m) * k, 1u, 1.f);
+  fill_pattern_kernel<<<592, 256, 0, stream>>>(b, static_cast<size_t>(k) * n, 2u, 0.03f);
+  fill_pattern_kernel<<<592, 256, 0, stream>>>(d, static_cast<size_t>(m) * n, 3u, 0.5f);
+  Problem pb;
+  pb.M = m;
+  pb.N = n;
+  pb.K = k;
+  pb.A = a;
+  pb.B = b;
+  pb.b_is_nk = b_is_nk;
+  pb.C = beta != 0.f ? d : nullptr;
+  pb.c_mode = beta != 0.f ? 1 : 0;
+  pb.D = d;
+  pb.alpha = alpha;
+  pb.beta = beta;
+  pb.act = act;
+  int best = 0;
+  float best_ms = 1e30f;
+  bool ok = true;
+  for (int row = 1; row <= kNumTileRows && ok; ++row) {
+    for (int i = 0; i < 3 && ok; ++i) ok = run(pb, row, stream);
+    if (!ok) break;
+    cudaEventRecord(e0, stream);
+    for (int i = 0; i < iters && ok; ++i) ok = run(pb, row, stream);
+    cudaEventRecord(e1, stream);
+    if (cudaEventSynchronize(e1) != cudaSuccess) ok = false;
+    float ms = 0.f;
+    if (ok) cudaEventElapsedTime(&ms, e0, e1);
+    const float us = 1e3f * ms / iters;
+    if (row_us) row_us[row - 1] = us;
+    if (ok && ms < best_ms) {
+      best_ms = ms;
+      best = row;
+    }
+  }
+  cleanup();
+  if (!ok || best == 0) return false;
+  {
+    std::lock_guard<std::mutex> lock(g_tuned_mutex);
+    g_tuned[TuneKey{m, n, k, act}] = best;
+  }
+  if (best_row) *best_row = best;
+  if (best_us) *best_us = 1e3f * best_ms / iters;
+  return true;
+}
+
 int select_tile_row(int64_t m, int64_t n, int64_t k, int act) {
   if (const char *env = std::getenv("HOM_GEMM_TILE")) {  // experiment knob
     const int v = std::atoi(env);
     if (v >= 1 && v <= kNumTileRows) return v;
   }
+  if (const int row = tuned_row(m, n, k, act)) return row;
   for (const ShapeRow &r : kShapeTable)
     if (r.m == m && r.n == n && r.k == k && r.act == act) return r.row;
   // Estimated time = waves x per-tile time.  A wave is 148 single-CTA tiles or 74 pair

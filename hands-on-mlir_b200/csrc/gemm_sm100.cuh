@@ -40,6 +40,14 @@ int select_tile_row(int64_t m, int64_t n, int64_t k, int act);
 int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, int *split_k);
 
 // Diagnostics, enabled by HOM_GEMM_PROFILE=1 only: per-role cycle counters of CTA 0.
+// Run-time tuner (GemmProfiler's contract): times the tile-table rows for one shape, remembers
+// the winner for later automatic selections, and can persist the table as text.
+bool tune(int64_t m, int64_t n, int64_t k, int act, float alpha, float beta, bool b_is_nk, int iters,
+          int *best_row, float *best_us, float *row_us, cudaStream_t stream);
+int tuned_row(int64_t m, int64_t n, int64_t k, int act);
+int tune_cache_load(const char *path);  // entries read, or -1
+int tune_cache_save(const char *path);  // entries written, or -1
+
 long long *profile_buffer();
 long long *profile_buffer_raw();  // the buffer if it exists; touches nothing
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream);

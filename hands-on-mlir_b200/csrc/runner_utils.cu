@@ -4,6 +4,9 @@
 // record an error (homGetLastError) and launch nothing.
 #include <cerrno>
 #include <cstdlib>
+#include <unistd.h>
+#include <sys/stat.h>
+#include <atomic>
 #include <cstring>
 #include <functional>
 #include <iostream>
@@ -126,11 +129,88 @@ bool read_constant_file(int32_t idx, std::vector<int64_t> *dims, std::vector<flo
   return true;
 }
 
+// ---- binary cache of parsed constants (opt-in: homSetConstantCache(1) or HOM_CONSTANT_CACHE=1).
+// Parsing the text of a BERT-sized weight set takes minutes; `<idx>.txt.homcache` beside the
+// text file holds the parsed fp32 values and is used while the text file's size and
+// modification time still match what the cache recorded.
+struct CacheHeader {
+  char magic[8];  // "HOMWGT1\0"
+  int64_t dims[3];
+  int64_t text_size;
+  int64_t text_mtime_ns;
+};
+std::atomic<int> g_constant_cache{-1};  // -1: consult the environment
+
+bool constant_cache_enabled() {
+  int v = g_constant_cache.load();
+  if (v < 0) {
+    const char *env = std::getenv("HOM_CONSTANT_CACHE");
+    v = (env && env[0] && env[0] != '0') ? 1 : 0;
+    g_constant_cache.store(v);
+  }
+  return v == 1;
+}
+
+bool stat_text(const std::string &path, int64_t *size, int64_t *mtime_ns) {
+  struct stat st;
+  if (::stat(path.c_str(), &st) != 0) return false;
+  *size = static_cast<int64_t>(st.st_size);
+  *mtime_ns = static_cast<int64_t>(st.st_mtim.tv_sec) * 1000000000LL + st.st_mtim.tv_nsec;
+  return true;
+}
+
+bool read_constant_cache(const std::string &text_path, std::vector<int64_t> *dims,
+                         std::vector<float> *values) {
+  int64_t size = 0, mtime = 0;
+  if (!stat_text(text_path, &size, &mtime)) return false;
+  FILE *f = std::fopen((text_path + ".homcache").c_str(), "rb");
+  if (!f) return false;
+  CacheHeader h;
+  bool ok = std::fread(&h, sizeof(h), 1, f) == 1 && std::memcmp(h.magic, "HOMWGT1", 8) == 0 &&
+            h.text_size == size && h.text_mtime_ns == mtime;
+  int64_t total = 1;
+  if (ok) {
+    for (int64_t d : h.dims) {
+      if (d < 0 || (d > 0 && total > (int64_t{1} << 40) / d)) ok = false;
+      else total *= d;
+    }
+  }
+  if (ok) {
+    values->resize(static_cast<size_t>(total));
+    ok = std::fread(values->data(), sizeof(float), values->size(), f) == values->size();
+  }
+  std::fclose(f);
+  if (ok) dims->assign(h.dims, h.dims + 3);
+  else values->clear();
+  return ok;
+}
+
+void write_constant_cache(const std::string &text_path, const std::vector<int64_t> &dims,
+                          const std::vector<float> &values) {
+  CacheHeader h{};
+  std::memcpy(h.magic, "HOMWGT1", 8);
+  for (int i = 0; i < 3; ++i) h.dims[i] = dims[i];
+  if (!stat_text(text_path, &h.text_size, &h.text_mtime_ns)) return;
+  const std::string final_path = text_path + ".homcache";
+  const std::string tmp_path = final_path + ".tmp" + std::to_string(static_cast<long long>(::getpid()));
+  FILE *f = std::fopen(tmp_path.c_str(), "wb");
+  if (!f) return;  // read-only weight directory: run without a cache
+  const bool ok = std::fwrite(&h, sizeof(h), 1, f) == 1 &&
+                  std::fwrite(values.data(), sizeof(float), values.size(), f) == values.size();
+  if (std::fclose(f) != 0 || !ok || std::rename(tmp_path.c_str(), final_path.c_str()) != 0)
+    std::remove(tmp_path.c_str());
+}
+
 template <typename T>
 HomUnrankedMemRef alloc_constant(int32_t idx) {
   std::vector<int64_t> dims;
   std::vector<float> values;
-  if (!read_constant_file(idx, &dims, &values)) return HomUnrankedMemRef{0, nullptr};
+  const bool cache = constant_cache_enabled();
+  if (!(cache && read_constant_cache(constant_path(idx), &dims, &values))) {
+    dims.clear();
+    if (!read_constant_file(idx, &dims, &values)) return HomUnrankedMemRef{0, nullptr};
+    if (cache) write_constant_cache(constant_path(idx), dims, values);
+  }
   HomUnrankedMemRef res = alloc_memref(dims, sizeof(T));
   if (!res.descriptor) return res;
   void *data = static_cast<void **>(res.descriptor)[1];
@@ -699,6 +779,8 @@ __attribute__((visibility("default"))) void homDebugReadProfile(long long *out, 
   if (buf && count > 0 && count <= 4096) cudaMemcpy(out, buf, count * sizeof(long long), cudaMemcpyDeviceToHost);
 }
 
+void homSetConstantCache(int enable) { g_constant_cache.store(enable ? 1 : 0); }
+
 void homSetConstantDir(const char *dir) {
   std::lock_guard<std::mutex> lock(g_dir_mutex);
   g_constant_dir = dir ? dir : "";
@@ -713,5 +795,27 @@ int32_t homGemmQueryTile(int64_t m, int64_t n, int64_t k, int64_t activation, in
   if (splitK) *splitK = sk;
   return row;
 }
+
+int32_t homGemmTune(int64_t m, int64_t n, int64_t k, int64_t activation, float alpha, float beta,
+                    int32_t weights_nk, int32_t iterations, int32_t *tile_row, int32_t *split_k,
+                    float *best_us, float *row_us) {
+  if (activation != 0 && activation != 1) {
+    hom::set_error(HOM_ERR_UNSUPPORTED, "homGemmTune: activation %lld is not supported",
+                   static_cast<long long>(activation));
+    return HOM_ERR_UNSUPPORTED;
+  }
+  int row = 0;
+  float us = 0.f;
+  if (!hom::gemm::tune(m, n, k, static_cast<int>(activation), alpha, beta, weights_nk != 0, iterations,
+                       &row, &us, row_us, hom::current_stream()))
+    return homGetLastError() ? homGetLastError() : HOM_ERR_CUDA;
+  if (tile_row) *tile_row = row;
+  if (split_k) *split_k = 1;
+  if (best_us) *best_us = us;
+  return 0;
+}
+
+int32_t homGemmTuneSave(const char *path) { return hom::gemm::tune_cache_save(path); }
+int32_t homGemmTuneLoad(const char *path) { return hom::gemm::tune_cache_load(path); }
 
 }  // extern "C"

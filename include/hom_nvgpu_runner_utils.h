@@ -184,6 +184,11 @@ HOM_EXPORT int homSynchronize(void);
 /* Directory that allocConstantNVGPU* reads "<idx>.txt" from (default: $HOM_CONSTANT_DIR,
  * else the current directory). */
 HOM_EXPORT void homSetConstantDir(const char *dir);
+/* Opt-in binary cache of parsed constants: with enable != 0 (or HOM_CONSTANT_CACHE=1)
+ * allocConstantNVGPU* writes `<idx>.txt.homcache` (parsed fp32 values) beside the text file on
+ * first use and reads it afterwards while the text file's size and modification time are
+ * unchanged.  A weight directory that cannot be written just runs uncached. */
+HOM_EXPORT void homSetConstantCache(int enable);
 
 /* Out = LayerNorm(X + R) * gamma + beta over the last dimension; X, R, Out [rows.., H]
  * fp16 (R, gamma, beta may be rank-0 descriptors = absent), fp32 sum and statistics,
@@ -233,6 +238,24 @@ HOM_EXPORT int64_t homOpTimingCollect(HomOpTiming *out, int64_t capacity);
  * pipeline stages and split-K.  Returns the tile-table row number (usable as gemmNum). */
 HOM_EXPORT int32_t homGemmQueryTile(int64_t m, int64_t n, int64_t k, int64_t activation,
                                     int32_t *bn, int32_t *stages, int32_t *splitK);
+
+/* Run-time tuner with the contract of GemmProfiler::profile
+ * (lib/NVGPUKernels/GemmProfiler.cu:143-236, include/NVGPUKernels/GemmProfiler.h:39-57): times every
+ * row of the tile table for fp16 (M, N, K, activation, alpha, beta) on scratch operands it
+ * allocates and frees (beta != 0 reads C = D), returns the fastest row in *tile_row (usable as
+ * gemmNum; the autotune pass writes it to `kernel_name`) and 1 in *split_k, and remembers the
+ * result so that later calls with an automatic gemmNum use it.  weights_nk != 0 times the
+ * [1,N,K] weight layout.  row_us, if not null, receives the six per-row times in microseconds.
+ * Blocks until the measurements are done; call it outside stream capture.  Returns the error
+ * code (0 = ok). */
+HOM_EXPORT int32_t homGemmTune(int64_t m, int64_t n, int64_t k, int64_t activation, float alpha,
+                               float beta, int32_t weights_nk, int32_t iterations,
+                               int32_t *tile_row, int32_t *split_k, float *best_us, float *row_us);
+/* The tuned table as text, one "M N K activation row" line per shape (the reference keeps its
+ * timing cache in memory only).  Return the number of entries, or -1 if the file cannot be
+ * opened.  $HOM_TUNE_CACHE names a file that is loaded on first use. */
+HOM_EXPORT int32_t homGemmTuneSave(const char *path);
+HOM_EXPORT int32_t homGemmTuneLoad(const char *path);
 
 #ifdef __cplusplus
 }

@@ -131,6 +131,21 @@ def test_tile_table_covers_the_bert_shapes(hom):
     assert big["row"] == 6 and big["bn"] == 256
 
 
+def test_tuned_table_round_trips_through_a_cache_file(hom, tmp_path):
+    """The tuned table (the stand-in for GemmProfiler's timing cache) overrides the built-in
+    choice, and what is saved is what is loaded."""
+    src = tmp_path / "tuned.txt"
+    src.write_text("1000 520 264 0 2\n1000 520 264 1 5\n77 8 8 0 9\n")  # row 9 is not a table row
+    assert hom.gemm_tune_load(src) == 2
+    assert hom.gemm_query_tile(1000, 520, 264, 0)["row"] == 2
+    assert hom.gemm_query_tile(1000, 520, 264, 1)["row"] == 5
+    out = tmp_path / "saved.txt"
+    assert hom.gemm_tune_save(out) >= 2
+    lines = {tuple(map(int, l.split())) for l in out.read_text().splitlines()}
+    assert (1000, 520, 264, 0, 2) in lines and (1000, 520, 264, 1, 5) in lines
+    assert hom.gemm_tune_load(tmp_path / "missing.txt") == -1
+
+
 def test_shard_batch(pkg):
     from hands_on_mlir_b200.bert_program import shard_batch
     spans = [shard_batch(256, 8, r) for r in range(8)]

@@ -336,6 +336,24 @@ def test_cu_seqlen_sizes(hom, cuda, oracle, dtype, bs, seq):
 
 # ------------------------------------------------------------ allocation / constants
 
+def test_gemm_tuner_picks_a_row_and_later_calls_use_it(hom, cuda, oracle, tmp_path):
+    """homGemmTune follows GemmProfiler::profile's contract: a row per (M, N, K, activation),
+    remembered for automatic selection; results do not depend on the row."""
+    m, n, k = 384, 520, 264
+    res = hom.gemm_tune(m, n, k, activation=1, alpha=1.0, beta=0.0, iterations=5)
+    assert 1 <= res["row"] <= 6 and res["split_k"] == 1
+    assert all(t > 0 for t in res["row_us"]) and abs(min(res["row_us"]) - res["best_us"]) < 1e-3
+    assert hom.gemm_query_tile(m, n, k, 1)["row"] == res["row"]
+    assert hom.gemm_tune_save(tmp_path / "t.txt") >= 1
+    rng = _rng(5)
+    A = rng.uniform(-1, 1, (1, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.05, (1, k, n)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, None, act=1, tile=0)
+    assert_close_f16(got, oracle.gemm_f16(A, B, act=1), "GEMM after tuning")
+    with pytest.raises(Exception):
+        hom.gemm_tune(m, n, 263, activation=0)  # K % 8 != 0 is rejected, nothing is launched
+
+
 def test_alloc_and_constant_loader(hom, cuda, oracle, tmp_path):
     import torch
     vals = _rng(2).normal(0, 0.02, (1, 24, 40)).astype(np.float32)
@@ -364,3 +382,45 @@ def test_alloc_and_constant_loader(hom, cuda, oracle, tmp_path):
     hom.dealloc("I32", d1)
     with pytest.raises(Exception):
         hom.allocConstantNVGPUF16(12345)  # missing file -> I/O error, no abort
+
+
+def test_constant_loader_binary_cache(hom, cuda, oracle, tmp_path):
+    """With the cache on, the second load comes from `<idx>.txt.homcache` bit for bit, and a
+    changed text file invalidates it."""
+    import os
+    import torch
+
+    def write(vals):
+        with open(tmp_path / "3.txt", "w") as f:
+            f.write("1 16 24\n")
+            f.write(" ".join(repr(float(v)) for v in vals.ravel()))
+            f.write("\n")
+
+    def load():
+        m = hom.allocConstantNVGPUF16(3)
+        buf = torch.empty((1, 16, 24), dtype=torch.float16, device=cuda)
+        rows = torch.arange(16, dtype=torch.int64, device=cuda).reshape(1, 16)
+        hom.gather("F16", rows, m, buf)
+        hom.synchronize()
+        hom.dealloc("F16", m)
+        return buf.cpu().numpy()
+
+    vals = _rng(8).normal(0, 0.5, (1, 16, 24)).astype(np.float32)
+    write(vals)
+    hom.lib.homSetConstantDir(str(tmp_path).encode())
+    hom.lib.homSetConstantCache(1)
+    try:
+        first = load()
+        cache = tmp_path / "3.txt.homcache"
+        assert cache.exists() and cache.stat().st_size == 48 + 4 * vals.size
+        want = oracle.f32_to_f16(oracle.parse_constant_text(tmp_path / "3.txt"))
+        assert_bits_equal(first, want, "constant, text parse")
+        stamp = cache.stat().st_mtime_ns
+        assert_bits_equal(load(), want, "constant, from the cache")
+        assert cache.stat().st_mtime_ns == stamp  # served from the cache, not rewritten
+        write(vals * 2)  # a new text file (other size / time) must not be served from the old cache
+        os.utime(tmp_path / "3.txt", ns=(stamp + 5_000_000_000, stamp + 5_000_000_000))
+        want2 = oracle.f32_to_f16(oracle.parse_constant_text(tmp_path / "3.txt"))
+        assert_bits_equal(load(), want2, "constant, cache invalidated")
+    finally:
+        hom.lib.homSetConstantCache(0)
