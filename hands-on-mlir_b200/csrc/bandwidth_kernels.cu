@@ -5,6 +5,8 @@
 //
 // They replace TransformerEngine's LayerNorm (include/NVGPUKernels/Layernorm.h:584-694) and
 // the Thrust pipelines of include/NVGPUKernels/{ElementwiseRunner,GatherRunner,CuSeqLen}.h.
+#include <cstdlib>
+
 #include "bandwidth_kernels.cuh"
 #include "ptx_sm100.cuh"
 
@@ -25,7 +27,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // y = (x [+ r] - mean) * rsqrt(var + eps) [* gamma] [+ beta]; statistics in fp32 with the
 // variance taken around the mean (two passes over registers).
 template <int VPT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 layernorm_f16_warp_kernel(const __half *x, const __half *res,
                           const __half *gamma, const __half *beta,
                           __half *out, long long rows, int hidden, float eps) {
@@ -419,8 +421,15 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
   const double bytes = 2.0 * rows * hidden * (2 + (res ? 1 : 0)) +
                        2.0 * hidden * ((gamma ? 1 : 0) + (beta ? 1 : 0));
   LaunchScope scope(kOpLayernorm, 0.0, bytes);
-  const int warps_per_block = 4;
+  // One launch wave of few, large blocks starts sooner (measured 4.4 vs 4.8 us at 4096 x 768);
+  // with many waves, small blocks retire and refill more evenly (5.27 vs 4.64 TB/s at 131072 rows).
+  int warps_per_block = rows <= 8192 ? 16 : 4;
+  if (const char *env = std::getenv("HOM_LN_WARPS")) {  // experiment knob
+    const int v = std::atoi(env);
+    if (v == 4 || v == 8 || v == 16) warps_per_block = v;
+  }
   const unsigned blocks = static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block);
+  const unsigned threads = 32u * warps_per_block;
   const bool vec_ok = hidden % 8 == 0 && hidden <= 32 * 8 * 16 && aligned16(x) && aligned16(out) &&
                       (!res || aligned16(res)) && (!gamma || aligned16(gamma)) &&
                       (!beta || aligned16(beta));
@@ -429,7 +438,7 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
     const int nvec = static_cast<int>(hidden / 8);
     const int vpt = (nvec + 31) / 32;
 #define HOM_LN_CASE(V)                                                                            \
-  err = launch_pdl(layernorm_f16_warp_kernel<V>, dim3(blocks), dim3(128), 0, stream, 1, x, res,   \
+  err = launch_pdl(layernorm_f16_warp_kernel<V>, dim3(blocks), dim3(threads), 0, stream, 1, x, res, \
                    gamma, beta, out, static_cast<long long>(rows), static_cast<int>(hidden), eps)
     if (vpt <= 1) HOM_LN_CASE(1);
     else if (vpt == 2) HOM_LN_CASE(2);
@@ -439,7 +448,7 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
     else HOM_LN_CASE(16);
 #undef HOM_LN_CASE
   } else {
-    err = launch_pdl(layernorm_generic_kernel<__half>, dim3(blocks), dim3(128), 0, stream, 1, x, res,
+    err = launch_pdl(layernorm_generic_kernel<__half>, dim3((rows + 3) / 4), dim3(128), 0, stream, 1, x, res,
                      gamma, beta, out, static_cast<long long>(rows), static_cast<int>(hidden), eps);
   }
   return check_cuda(err, "layernorm kernel launch") &&
