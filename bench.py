@@ -446,7 +446,7 @@ def run_gpu_arm(args, cfg, workload):
         local_batch, first, global_batch = hi - lo, lo, workload["batch"]
     seq = workload["seq"]
 
-    prog = BertProgram(cfg, local_batch, seq)
+    prog = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding)
     weights = make_weights_torch(cfg, seq, device)
     prog.set_weights(weights)
     ids_np, mask_np, types_np = make_inputs(workload, local_batch, first)
@@ -588,7 +588,8 @@ def run_gpu_arm(args, cfg, workload):
                 "parallelism": f"batch-sharded replicas x{world}, no data-path collective",
                 "l2": "no explicit flush: the per-step working set (all layer weights + "
                       "activations) exceeds the 126 MB L2",
-                "launch": "CUDA-graph replay of the runner-utils call sequence",
+                "launch": "CUDA-graph replay of the runner-utils call sequence"
+                          + (" with the fused embedding extension" if args.fused_embedding else ""),
             },
             "model_tflops": value * flops_per_seq / 1e12,
             "e2e": {"value": e2e_value, "unit": "sequences/s", "h2d_bytes_per_step": h2d,
@@ -616,6 +617,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bert-base")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused-embedding", action="store_true",
+                    help="replace the five embedding calls by homBertEmbeddingF16 (same bits; not "
+                         "the call sequence the reference's lowering emits, so off by default)")
     ap.add_argument("--op", choices=sorted(OP_CASES), default=None,
                     help="time one kernel of the path on its own instead of the whole encoder")
     ap.add_argument("--tile", type=int, default=0,

@@ -136,6 +136,7 @@ _SIGNATURES = {
     "homSynchronize": (ctypes.c_int, []),
     "homSetConstantDir": (None, [c_char_p]),
     "homResidualLayernormF16": (None, _MEMREF * 5 + [c_float]),
+    "homBertEmbeddingF16": (None, _MEMREF * 6 + [c_float]),
     "homLayernormGemmF16NoAlloc": (None, _MEMREF * 6 + [c_float, c_float]),
     "homKernelLaunchCount": (c_int64, []),
     "homOpTimingEnable": (None, [ctypes.c_int]),
@@ -243,6 +244,11 @@ class RunnerUtils:
     def homResidualLayernormF16(self, X, R, gamma, beta, Out, eps=1e-12):
         self.lib.homResidualLayernormF16(*_as_args(X), *_as_args(R), *_as_args(gamma),
                                          *_as_args(beta), *_as_args(Out), eps)
+        self.check()
+
+    def homBertEmbeddingF16(self, ids, types, word, pos, type_emb, Out, eps=1e-12):
+        self.lib.homBertEmbeddingF16(*_as_args(ids), *_as_args(types), *_as_args(word), *_as_args(pos),
+                                     *_as_args(type_emb), *_as_args(Out), eps)
         self.check()
 
     def nvteBertAttentionF16(self, qkv, cu_seqlens, out, scale, headNum):

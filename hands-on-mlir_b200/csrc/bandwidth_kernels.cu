@@ -26,11 +26,22 @@ __device__ __forceinline__ float warp_sum(float v) {
 // One warp per row; the row lives in registers as VPT 16-byte vectors per lane.
 // y = (x [+ r] - mean) * rsqrt(var + eps) [* gamma] [+ beta]; statistics in fp32 with the
 // variance taken around the mean (two passes over registers).
-template <int VPT>
+// With EMBED the row is not read from `x` but assembled from three embedding tables:
+// word[ids[row]] + type[types[row]], rounded to fp16, + pos[row % seq], rounded to fp16 - the
+// values the separate gather / add / add calls would have left in memory - and then normalised
+// by the same code, so the fused kernel reproduces the five-call sequence bit for bit.
+struct EmbedArgs {
+  const long long *ids = nullptr, *types = nullptr;
+  const __half *type_emb = nullptr, *pos_emb = nullptr;
+  long long vocab = 0, type_vocab = 0;
+  int seq = 1;
+};
+
+template <int VPT, bool EMBED>
 __global__ void __launch_bounds__(512)
 layernorm_f16_warp_kernel(const __half *x, const __half *res,
                           const __half *gamma, const __half *beta,
-                          __half *out, long long rows, int hidden, float eps) {
+                          __half *out, long long rows, int hidden, float eps, const EmbedArgs emb) {
   hom::ptx::pdl_launch_dependents();
   hom::ptx::pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -39,6 +50,16 @@ layernorm_f16_warp_kernel(const __half *x, const __half *res,
   const int nvec = hidden >> 3;
   const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * hidden);
   const uint4 *rr = res ? reinterpret_cast<const uint4 *>(res + row * hidden) : nullptr;
+  const uint4 *tr = nullptr, *pr = nullptr;
+  bool word_ok = true, type_ok = true;
+  if (EMBED) {
+    const long long id = emb.ids[row], ty = emb.types[row];
+    word_ok = id >= 0 && id < emb.vocab;  // out-of-range indices read as zero rows, like the gather
+    type_ok = ty >= 0 && ty < emb.type_vocab;
+    xr = reinterpret_cast<const uint4 *>(x + (word_ok ? id : 0) * hidden);
+    tr = reinterpret_cast<const uint4 *>(emb.type_emb + (type_ok ? ty : 0) * hidden);
+    pr = reinterpret_cast<const uint4 *>(emb.pos_emb + (row % emb.seq) * hidden);
+  }
 
   float v[VPT][8];
   float sum = 0.f;
@@ -46,7 +67,19 @@ layernorm_f16_warp_kernel(const __half *x, const __half *res,
   for (int i = 0; i < VPT; ++i) {
     const int vi = lane + 32 * i;
     if (vi < nvec) {
-      const uint4 raw = xr[vi];
+      uint4 raw = xr[vi];
+      if (EMBED) {
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        if (!word_ok) raw = zero;
+        uint4 raw_t = tr[vi];
+        if (!type_ok) raw_t = zero;
+        const uint4 raw_p = pr[vi];
+        __half2 *w2 = reinterpret_cast<__half2 *>(&raw);
+        const __half2 *t2 = reinterpret_cast<const __half2 *>(&raw_t);
+        const __half2 *p2 = reinterpret_cast<const __half2 *>(&raw_p);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w2[j] = __hadd2(__hadd2(w2[j], t2[j]), p2[j]);
+      }
       const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -438,8 +471,9 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
     const int nvec = static_cast<int>(hidden / 8);
     const int vpt = (nvec + 31) / 32;
 #define HOM_LN_CASE(V)                                                                            \
-  err = launch_pdl(layernorm_f16_warp_kernel<V>, dim3(blocks), dim3(threads), 0, stream, 1, x, res, \
-                   gamma, beta, out, static_cast<long long>(rows), static_cast<int>(hidden), eps)
+  err = launch_pdl(layernorm_f16_warp_kernel<V, false>, dim3(blocks), dim3(threads), 0, stream, 1, x, \
+                   res, gamma, beta, out, static_cast<long long>(rows), static_cast<int>(hidden),  \
+                   eps, EmbedArgs{})
     if (vpt <= 1) HOM_LN_CASE(1);
     else if (vpt == 2) HOM_LN_CASE(2);
     else if (vpt == 3) HOM_LN_CASE(3);
@@ -453,6 +487,41 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
   }
   return check_cuda(err, "layernorm kernel launch") &&
          check_cuda(cudaGetLastError(), "layernorm kernel launch");
+}
+
+bool embedding_layernorm_f16(const int64_t *ids, const int64_t *types, const __half *word_emb,
+                             const __half *pos_emb, const __half *type_emb, __half *out, int64_t rows,
+                             int64_t seq, int64_t hidden, int64_t vocab, int64_t type_vocab, float eps,
+                             cudaStream_t stream) {
+  if (rows == 0 || hidden == 0) return true;
+  // per row: two indices, three table rows read, one row written
+  LaunchScope scope(kOpLayernorm, 0.0, rows * (16.0 + 2.0 * hidden * 4));
+  const int warps_per_block = rows <= 8192 ? 16 : 4;
+  const unsigned blocks = static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block);
+  const unsigned threads = 32u * warps_per_block;
+  EmbedArgs emb;
+  emb.ids = reinterpret_cast<const long long *>(ids);
+  emb.types = reinterpret_cast<const long long *>(types);
+  emb.type_emb = type_emb;
+  emb.pos_emb = pos_emb;
+  emb.vocab = vocab;
+  emb.type_vocab = type_vocab;
+  emb.seq = static_cast<int>(seq);
+  const __half *none = nullptr;
+  const int vpt = (static_cast<int>(hidden / 8) + 31) / 32;
+  cudaError_t err = cudaSuccess;
+#define HOM_EMB_CASE(V)                                                                           \
+  err = launch_pdl(layernorm_f16_warp_kernel<V, true>, dim3(blocks), dim3(threads), 0, stream, 1,  \
+                   word_emb, none, none, none, out, static_cast<long long>(rows),                  \
+                   static_cast<int>(hidden), eps, emb)
+  if (vpt <= 1) HOM_EMB_CASE(1);
+  else if (vpt == 2) HOM_EMB_CASE(2);
+  else if (vpt == 3) HOM_EMB_CASE(3);
+  else if (vpt == 4) HOM_EMB_CASE(4);
+  else if (vpt <= 8) HOM_EMB_CASE(8);
+  else HOM_EMB_CASE(16);
+#undef HOM_EMB_CASE
+  return check_cuda(err, "embedding kernel launch");
 }
 
 bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, float eps,

@@ -17,6 +17,13 @@ struct BroadcastShape {
 // out = LayerNorm(x [+ res]) [* gamma] [+ beta]; res/gamma/beta may be null; out may alias x.
 bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, const __half *beta,
                    __half *out, int64_t rows, int64_t hidden, float eps, cudaStream_t stream);
+// out[row] = LayerNorm(fp16(fp16(word[ids[row]] + type[types[row]]) + pos[row % seq])), no affine:
+// the embedding stage of the encoder in one pass.  hidden must be a multiple of 8 and at most
+// 4096, all tables 16-byte aligned.
+bool embedding_layernorm_f16(const int64_t *ids, const int64_t *types, const __half *word_emb,
+                             const __half *pos_emb, const __half *type_emb, __half *out, int64_t rows,
+                             int64_t seq, int64_t hidden, int64_t vocab, int64_t type_vocab, float eps,
+                             cudaStream_t stream);
 bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, float eps,
                    cudaStream_t stream);
 

@@ -95,13 +95,19 @@ int issue_forward(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void
                      d.desc, act, 1.0f, beta, 0, 1);
   };
   thrustCuSeqLenI64(rankMask, mask, p.cu.rank, p.cu.desc);
-  thrustGatherF16(rankIds, ids, p.weights[0].rank, p.weights[0].desc, p.x.rank, p.x.desc);
-  thrustGatherF16(rankTypes, types, p.weights[2].rank, p.weights[2].desc, p.type_rows.rank,
-                  p.type_rows.desc);
-  thrustElementwiseAddF16(p.x.rank, p.x.desc, p.type_rows.rank, p.type_rows.desc, p.x.rank, p.x.desc);
-  thrustElementwiseAddF16(p.x.rank, p.x.desc, p.weights[1].rank, p.weights[1].desc, p.x.rank,
-                          p.x.desc);
-  nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+  if (c.fused_embedding) {
+    homBertEmbeddingF16(rankIds, ids, rankTypes, types, p.weights[0].rank, p.weights[0].desc,
+                        p.weights[1].rank, p.weights[1].desc, p.weights[2].rank, p.weights[2].desc,
+                        p.x.rank, p.x.desc, c.eps);
+  } else {
+    thrustGatherF16(rankIds, ids, p.weights[0].rank, p.weights[0].desc, p.x.rank, p.x.desc);
+    thrustGatherF16(rankTypes, types, p.weights[2].rank, p.weights[2].desc, p.type_rows.rank,
+                    p.type_rows.desc);
+    thrustElementwiseAddF16(p.x.rank, p.x.desc, p.type_rows.rank, p.type_rows.desc, p.x.rank, p.x.desc);
+    thrustElementwiseAddF16(p.x.rank, p.x.desc, p.weights[1].rank, p.weights[1].desc, p.x.rank,
+                            p.x.desc);
+    nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+  }
   for (int l = 0; l < c.layers; ++l) {
     Tensor &wqkv = p.weights[3 + 4 * l], &wo = p.weights[4 + 4 * l];
     Tensor &w1 = p.weights[5 + 4 * l], &w2 = p.weights[6 + 4 * l];
@@ -361,7 +367,7 @@ void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d2h_bytes) {
 
 int32_t homBertLaunchesPerForward(void *program) {
   auto *p = static_cast<Program *>(program);
-  return p ? 6 + 7 * p->cfg.layers : 0;
+  return p ? (p->cfg.fused_embedding ? 2 : 6) + 7 * p->cfg.layers : 0;
 }
 
 }  // extern "C"

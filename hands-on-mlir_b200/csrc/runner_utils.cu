@@ -666,6 +666,50 @@ void homResidualLayernormF16(int64_t rankX, void *dstX, int64_t rankR, void *dst
                          hom::current_stream());
 }
 
+void homBertEmbeddingF16(int64_t rankIds, void *dstIds, int64_t rankTypes, void *dstTypes,
+                         int64_t rankWord, void *dstWord, int64_t rankPos, void *dstPos,
+                         int64_t rankTypeEmb, void *dstTypeEmb, int64_t rankOut, void *dstOut,
+                         float eps) {
+  const char *name = "homBertEmbeddingF16";
+  MemRefView I = view_memref(rankIds, dstIds, 8), T = view_memref(rankTypes, dstTypes, 8);
+  MemRefView W = view_memref(rankWord, dstWord, 2), P = view_memref(rankPos, dstPos, 2);
+  MemRefView E = view_memref(rankTypeEmb, dstTypeEmb, 2), O = view_memref(rankOut, dstOut, 2);
+  if (!I.valid || !T.valid || !W.valid || !P.valid || !E.valid || !O.valid) {
+    set_error(HOM_ERR_INVALID, "%s: null or malformed descriptor", name);
+    return;
+  }
+  if (I.rank != 2 || T.rank != 2 || W.rank != 3 || P.rank != 3 || E.rank != 3 || O.rank != 3 ||
+      W.sizes[0] != 1 || P.sizes[0] != 1 || E.sizes[0] != 1) {
+    set_error(HOM_ERR_INVALID,
+              "%s: expects ids, types [bs,seq]; word [1,V,H], pos [1,seq,H], type [1,T,H]; out [bs,seq,H]",
+              name);
+    return;
+  }
+  const int64_t bs = I.sizes[0], seq = I.sizes[1], hidden = O.sizes[2];
+  if (T.sizes[0] != bs || T.sizes[1] != seq || O.sizes[0] != bs || O.sizes[1] != seq ||
+      W.sizes[2] != hidden || E.sizes[2] != hidden || P.sizes[2] != hidden || P.sizes[1] != seq) {
+    set_error(HOM_ERR_INVALID, "%s: shapes of the indices, tables and output do not agree", name);
+    return;
+  }
+  if (!I.contiguous() || !T.contiguous() || !W.contiguous() || !P.contiguous() || !E.contiguous() ||
+      !O.contiguous()) {
+    set_error(HOM_ERR_INVALID, "%s: operands must be row-major contiguous", name);
+    return;
+  }
+  auto aligned = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (hidden % 8 != 0 || hidden > 4096 || !aligned(W.ptr) || !aligned(P.ptr) || !aligned(E.ptr) ||
+      !aligned(O.ptr)) {
+    set_error(HOM_ERR_UNSUPPORTED,
+              "%s: hidden must be a multiple of 8, at most 4096, and the tables 16-byte aligned", name);
+    return;
+  }
+  hom::bw::embedding_layernorm_f16(
+      reinterpret_cast<const int64_t *>(I.ptr), reinterpret_cast<const int64_t *>(T.ptr),
+      reinterpret_cast<const __half *>(W.ptr), reinterpret_cast<const __half *>(P.ptr),
+      reinterpret_cast<const __half *>(E.ptr), reinterpret_cast<__half *>(O.ptr), bs * seq, seq, hidden,
+      W.sizes[1], E.sizes[1], eps, hom::current_stream());
+}
+
 void nvteBertAttentionF16(int64_t rankA, void *dstA, int64_t rankSeqlen, void *dstSeqlen,
                           int64_t rankOut, void *dstOut, float scale, int64_t headNum) {
   MemRefView A = view_memref(rankA, dstA, 2), S = view_memref(rankSeqlen, dstSeqlen, 4);

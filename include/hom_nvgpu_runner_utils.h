@@ -190,6 +190,17 @@ HOM_EXPORT void homSetConstantDir(const char *dir);
  * unchanged.  A weight directory that cannot be written just runs uncached. */
 HOM_EXPORT void homSetConstantCache(int enable);
 
+/* The embedding stage of the lowered BERT in one launch: what the five calls
+ * thrustGatherF16(ids, word) ; thrustGatherF16(types, typeEmb) ; thrustElementwiseAddF16 x2 ;
+ * nvteLayernormF16 leave in Out, bit for bit (each fp16 addition rounded, fp32 statistics, no
+ * affine).  ids, types int64 [bs,seq]; word [1,V,H], pos [1,seq,H], typeEmb [1,T,H], Out
+ * [bs,seq,H] fp16; out-of-range indices read as zero rows.  No counterpart in the reference:
+ * a compiler pass would have to emit it in place of the five calls. */
+HOM_EXPORT void homBertEmbeddingF16(int64_t rankIds, void *dstIds, int64_t rankTypes, void *dstTypes,
+                                    int64_t rankWord, void *dstWord, int64_t rankPos, void *dstPos,
+                                    int64_t rankTypeEmb, void *dstTypeEmb, int64_t rankOut,
+                                    void *dstOut, float eps);
+
 /* Out = LayerNorm(X + R) * gamma + beta over the last dimension; X, R, Out [rows.., H]
  * fp16 (R, gamma, beta may be rank-0 descriptors = absent), fp32 sum and statistics,
  * one fp16 rounding at the store.  Out may alias X. */

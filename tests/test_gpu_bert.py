@@ -120,6 +120,54 @@ def test_init_from_constant_files(hom, cuda, oracle, tmp_path):
     prog.close()
 
 
+def test_fused_embedding_reproduces_the_five_call_sequence(hom, cuda, oracle):
+    """homBertEmbeddingF16 against the gather / gather / add / add / LayerNorm calls it stands
+    for: same bits on the op itself (out-of-range indices included) and on a whole forward."""
+    import torch
+    from hands_on_mlir_b200.bert_program import BertProgram
+    rng = np.random.Generator(np.random.PCG64(21))
+    B, S, H, V = 3, 40, 264, 500
+    word, pos, typ = f16(rng.normal(0, 1, (1, V, H))), f16(rng.normal(0, 1, (1, S, H))), f16(rng.normal(0, 1, (1, 2, H)))
+    ids = rng.integers(0, V, (B, S)).astype(np.int64)
+    types = rng.integers(0, 2, (B, S)).astype(np.int64)
+    ids[0, 3], ids[1, 7], types[2, 5] = -1, V, 2  # read as zero rows by both paths
+    tw, tp, tt = to_dev(word, cuda), to_dev(pos, cuda), to_dev(typ, cuda)
+    ti, ty = to_dev(ids, cuda), to_dev(types, cuda)
+    x = torch.empty((B, S, H), dtype=torch.float16, device=cuda)
+    rows = torch.empty_like(x)
+    hom.gather("F16", ti, tw, x)
+    hom.gather("F16", ty, tt, rows)
+    hom.elementwise("Add", "F16", x, rows, x)
+    hom.elementwise("Add", "F16", x, tp, x)
+    hom.nvteLayernormF16(x, 1e-12)
+    fused = torch.full_like(x, float("nan"))
+    before = hom.launch_count()
+    hom.homBertEmbeddingF16(ti, ty, tw, tp, tt, fused, 1e-12)
+    assert hom.launch_count() - before == 1
+    hom.synchronize()
+    assert_bits_equal(fused.cpu().numpy(), x.cpu().numpy(), "fused embedding vs five calls")
+    want = oracle.layernorm_f16(oracle.elementwise("Add", oracle.elementwise(
+        "Add", oracle.gather(ids, word), oracle.gather(types, typ)), pos), eps=1e-12)
+    from util import assert_close_f16
+    assert_close_f16(fused.cpu().numpy(), want, "fused embedding vs oracle")
+
+    cfg, w, rng = tiny_model(4, L=1)
+    B, S = 2, 128
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = np.ones((B, S), dtype=np.int64)
+    types = rng.integers(0, 2, (B, S)).astype(np.int64)
+    outs = []
+    for fused_flag in (False, True):
+        prog = BertProgram(cfg, B, S, fused_embedding=fused_flag)
+        prog.set_weights({k: to_dev(v, cuda) for k, v in w.items()})
+        assert prog.launches_per_forward() == (2 if fused_flag else 6) + 7 * cfg.layers
+        res = prog.forward(to_dev(ids, cuda), to_dev(mask, cuda), to_dev(types, cuda))
+        outs.append(prog.result_to_torch(res).cpu().numpy())
+        hom.synchronize()
+        prog.close()
+    assert_bits_equal(outs[1], outs[0], "forward with the fused embedding")
+
+
 def test_nk_weight_layout_path(hom, cuda, oracle):
     """The TransformerEngine-style path: weights stored [1,N,K], GEMMs through nvteGemmF16."""
     from hands_on_mlir_b200.bert_program import BertProgram
