@@ -53,6 +53,9 @@ struct PairParams {
   int b_grouped;  // B [K,N] is fetched through the grouped 3-D tensor map (N % 64 == 0)
   int *status;
   long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
+  int dbg;          // profile-mode experiments (HOM_GEMM_DBG): 1 no barrier probe, 2 epilogue only
+                    // releases the accumulator, 4 no loads / no stage hand-offs (MMA issue alone),
+                    // 8 no per-block tcgen05 fence; results are garbage with 2 and 4
 };
 
 template <int BN2, bool B_NK>
@@ -109,35 +112,42 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_tensormap(&tmA);
-      prefetch_tensormap(&tmB);
+    // Run by the whole warp (coordinates and addresses stay warp-uniform); one elected lane
+    // arms the barriers and issues the copies.
+    {
+      const bool leader = elect_one();
+      if (leader) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+      }
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
       long long t_wait = 0, t_begin = clock64();
+      const uint32_t full_even_base = map_to_cta(full_bar(0), 0);
+      auto full_even = [&](int slot) { return full_even_base + 8u * slot; };
       auto arm = [&](int slot) {
         // The even CTA's producer arms the barrier for the bytes of both CTAs; the odd CTA's
         // copies only count their bytes on it.
-        if (rank == 0) mbar_arrive_expect_tx(full_bar(slot), 2 * Cfg::kStageBytes);
+        if (rank == 0 && leader) mbar_arrive_expect_tx(full_bar(slot), 2 * Cfg::kStageBytes);
       };
       auto load_b = [&](int slot, int kb, int nb0) {
-        const uint32_t full_even = map_to_cta(full_bar(slot), 0);
         const uint32_t b_dst = smem_base + slot * Cfg::kStageBytes + kABytes;
+        if (!leader) return;
         if (B_NK) {
-          tma_load_2d_pair(b_dst, &tmB, full_even, kb * BK, nb0);
+          tma_load_2d_pair(b_dst, &tmB, full_even(slot), kb * BK, nb0);
         } else if (p.b_grouped) {
-          tma_load_3d_pair(b_dst, &tmB, full_even, 0, kb * BK, nb0 / 64);
+          tma_load_3d_pair(b_dst, &tmB, full_even(slot), 0, kb * BK, nb0 / 64);
         } else {
 #pragma unroll
           for (int g = 0; g < HALF / 64; ++g)
-            tma_load_2d_pair(b_dst + g * (BK * 128), &tmB, full_even, nb0 + g * 64, kb * BK);
+            tma_load_2d_pair(b_dst + g * (BK * 128), &tmB, full_even(slot), nb0 + g * 64, kb * BK);
         }
       };
       // B holds weights, which no earlier kernel of the stream writes: the first ring of B
       // tiles is requested before waiting for the previous kernel, A only after.
       int pre = 0;
-      if (pair < p.num_tiles) {
+      if (pair < p.num_tiles && !(p.dbg & 4)) {
         const int nb0 = (pair % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
         pre = p.num_kb < stages_used ? p.num_kb : stages_used;
         for (int kb = 0; kb < pre; ++kb) {
@@ -146,30 +156,28 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
       }
       pdl_wait();
-      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+      for (int tile = pair; tile < p.num_tiles && ok && !(p.dbg & 4); tile += num_pairs) {
         const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
         const int nb0 = (tile % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           const bool b_done = tile == pair && kb < pre;
           if (!b_done) {
             const long long tw = p.prof ? clock64() : 0;
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutProducer)) {
-              ok = false;
-              break;
-            }
+            ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status,
+                                                   kDevWaitTimeoutProducer));
+            if (!ok) break;
             if (p.prof) t_wait += clock64() - tw;
             arm(s);
             load_b(s, kb, nb0);
           }
-          tma_load_2d_pair(smem_base + s * Cfg::kStageBytes, &tmA, map_to_cta(full_bar(s), 0), kb * BK,
-                           m0);
+          if (leader) tma_load_2d_pair(smem_base + s * Cfg::kStageBytes, &tmA, full_even(s), kb * BK, m0);
           if (++s == stages_used) {
             s = 0;
             ph ^= 1u;
           }
         }
       }
-      if (p.prof && blockIdx.x < 2) {
+      if (p.prof && blockIdx.x < 2 && lane == 0) {
         p.prof[0 + 8 * blockIdx.x] = clock64() - t_begin;
         p.prof[1 + 8 * blockIdx.x] = t_wait;
       }
@@ -182,8 +190,11 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   } else if (warp == 1) {
     // ------------------------------------------------- MMA issuer (even CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop so that stage addresses and descriptors stay warp-uniform;
+    // one elected lane issues the MMAs and the commits.
+    if (rank == 0) {
       constexpr uint32_t idesc = make_idesc_f16(256, BN2, false, !B_NK);
+      const bool leader = elect_one();
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -193,22 +204,23 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
         const long long ta = p.prof ? clock64() : 0;
-        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma)) break;
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma));
+        if (!ok) break;
         if (p.prof) t_acc += clock64() - ta;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN2;
         bool have = false;  // full[s] already seen complete by the probe of the previous block
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!have) {
+          if (!have && !(p.dbg & 4)) {
             const long long tw = p.prof ? clock64() : 0;
-            if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma)) {
-              ok = false;
-              break;
-            }
+            ok = __all_sync(0xffffffffu,
+                            mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma));
+            if (!ok) break;
             if (p.prof) t_full += clock64() - tw;
           }
           have = false;
-          tc_fence_after_sync();
+          if (!(p.dbg & 8)) tc_fence_after_sync();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + kABytes;
           const int s_next = s + 1 == stages_used ? 0 : s + 1;
@@ -218,17 +230,18 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const uint64_t da = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t db = B_NK ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                      : make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024);
-            tc_mma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (leader) tc_mma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             // Probe the next stage while the tensor pipe is busy with what was just queued.
-            if (k == 1 && kb + 1 < p.num_kb) have = mbar_test_wait(full_bar(s_next), ph_next);
+            if (k == 1 && kb + 1 < p.num_kb && !(p.dbg & 5))
+              have = __all_sync(0xffffffffu, mbar_test_wait(full_bar(s_next), ph_next));
           }
-          tc_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
+          if (leader && !(p.dbg & 4)) tc_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
           s = s_next;
           ph = ph_next;
         }
-        if (ok) tc_commit_pair(tfull_bar(acc), 0x3);  // accumulator ready in both CTAs
+        if (ok && leader) tc_commit_pair(tfull_bar(acc), 0x3);  // accumulator ready in both CTAs
       }
-      if (p.prof && blockIdx.x == 0) {
+      if (p.prof && blockIdx.x == 0 && lane == 0) {
         p.prof[2] = clock64() - t_begin;
         p.prof[3] = t_full;
         p.prof[4] = t_acc;
@@ -256,6 +269,15 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       if (!ok) break;
       if (p.prof) t_wait += clock64() - tw;
       tc_fence_after_sync();
+      if (p.dbg & 2) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(tempty_bar(acc));
+          else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+        }
+        continue;
+      }
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_half * HALF;
       epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, HALF, stage_smem, lane, n_stores,
@@ -374,6 +396,10 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   }
   p.status = device_status_word();
   p.prof = profile_buffer();
+  p.dbg = 0;
+  if (p.prof) {
+    if (const char *env = std::getenv("HOM_GEMM_DBG")) p.dbg = std::atoi(env);
+  }
   const int pairs = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
   cfg.gridDim = dim3(2 * pairs);
   const double flops = 2.0 * pb.M * pb.N * pb.K;

@@ -126,15 +126,21 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_tensormap(&tmA);
-      prefetch_tensormap(&tmB);
+    // Run by the whole warp (coordinates and addresses stay warp-uniform); one elected lane
+    // arms the barriers and issues the copies.
+    {
+      const bool leader = elect_one();
+      if (leader) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+      }
       int s = 0;
       uint32_t ph = 0, armed = 0;
       bool ok = true;
       long long t_wait = 0, t_begin = clock64();
       auto load_b = [&](int slot, int kb, int n0) {
         const uint32_t b_dst = smem_base + slot * Cfg::kStageBytes + kABytes;
+        if (!leader) return;
         if (B_NK) {
           tma_load_2d(b_dst, &tmB, full_bar(slot), kb * BK, n0);
         } else if (p.b_grouped) {
@@ -152,7 +158,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int n0 = (blockIdx.x % p.n_blocks) * BN;
         pre = p.num_kb < stages_used ? p.num_kb : stages_used;
         for (int kb = 0; kb < pre; ++kb) {
-          mbar_arrive_expect_tx(full_bar(kb), Cfg::kStageBytes);
+          if (leader) mbar_arrive_expect_tx(full_bar(kb), Cfg::kStageBytes);
           load_b(kb, kb, n0);
         }
       }
@@ -164,15 +170,14 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const bool b_done = tile == static_cast<int>(blockIdx.x) && kb < pre;
           if (!b_done) {
             const long long tw = p.prof ? clock64() : 0;
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutProducer)) {
-              ok = false;
-              break;
-            }
+            ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status,
+                                                   kDevWaitTimeoutProducer));
+            if (!ok) break;
             if (p.prof) t_wait += clock64() - tw;
-            mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
+            if (leader) mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
             load_b(s, kb, n0);
           }
-          tma_load_2d(smem_base + s * Cfg::kStageBytes, &tmA, full_bar(s), kb * BK, m0);
+          if (leader) tma_load_2d(smem_base + s * Cfg::kStageBytes, &tmA, full_bar(s), kb * BK, m0);
           ++armed;
           if (++s == stages_used) {
             s = 0;
@@ -180,12 +185,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
       }
-      if (p.prof && blockIdx.x == 0) {
+      if (p.prof && blockIdx.x == 0 && lane == 0) {
         p.prof[0] = clock64() - t_begin;
         p.prof[1] = t_wait;
       }
       if (!ok) {
-        // Let every copy this thread started land before the CTA gives its shared memory back.
+        // Let every copy this warp started land before the CTA gives its shared memory back.
         for (int st = 0; st < stages_used; ++st) {
           const uint32_t n_st = armed / stages_used + (static_cast<uint32_t>(st) < armed % stages_used ? 1u : 0u);
           if (n_st > 0) mbar_wait_drain(full_bar(st), (n_st - 1u) & 1u);
@@ -194,8 +199,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop so that stage addresses and descriptors stay warp-uniform;
+    // one elected lane issues the MMAs and the commits.
+    {
       constexpr uint32_t idesc = make_idesc_f16(BM, BN, false, !B_NK);
+      const bool leader = elect_one();
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -205,7 +213,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
         const long long ta = p.prof ? clock64() : 0;
-        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma)) break;
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma));
+        if (!ok) break;
         if (p.prof) t_acc += clock64() - ta;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -213,10 +223,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!have) {
             const long long tw = p.prof ? clock64() : 0;
-            if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma)) {
-              ok = false;
-              break;
-            }
+            ok = __all_sync(0xffffffffu,
+                            mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma));
+            if (!ok) break;
             if (p.prof) t_full += clock64() - tw;
           }
           have = false;
@@ -234,17 +243,18 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // = 2048 B.
             const uint64_t db = B_NK ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                      : make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024);
-            tc_mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (leader) tc_mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             // Probe the next stage while the tensor pipe is busy with what was just queued.
-            if (k == 1 && kb + 1 < p.num_kb) have = mbar_test_wait(full_bar(s_next), ph_next);
+            if (k == 1 && kb + 1 < p.num_kb)
+              have = __all_sync(0xffffffffu, mbar_test_wait(full_bar(s_next), ph_next));
           }
-          tc_commit(empty_bar(s));
+          if (leader) tc_commit(empty_bar(s));
           s = s_next;
           ph = ph_next;
         }
-        if (ok) tc_commit(tfull_bar(acc));
+        if (ok && leader) tc_commit(tfull_bar(acc));
       }
-      if (p.prof && blockIdx.x == 0) {
+      if (p.prof && blockIdx.x == 0 && lane == 0) {
         p.prof[2] = clock64() - t_begin;
         p.prof[3] = t_full;
         p.prof[4] = t_acc;

@@ -16,6 +16,9 @@ namespace ptx {
 
 // ~1.5 s at 1.9 GHz. Far beyond any legitimate wait in these kernels.
 constexpr long long kWaitLimitCycles = 3000000000LL;
+// Upper bound of one hardware-suspended poll inside a bounded wait (the abort flag and the
+// cycle limit are looked at every 64 polls).
+constexpr uint32_t kWaitSuspendNs = 20000;
 
 // Error codes written to the status word by device code.
 enum DeviceError : int {
@@ -31,6 +34,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of the (converged) warp gets true.  Code that is executed by the whole warp with
+// only the asynchronous instruction itself under this predicate keeps its address and
+// descriptor arithmetic warp-uniform, which is what lets it run on the uniform datapath.
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(
@@ -96,6 +102,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// try_wait with a suspend-time hint: the thread may stay suspended in hardware for up to
+// `ns` nanoseconds (instead of the short system default) and is woken when the phase
+// completes, so a waiting warp does not take issue slots from the warps that share its
+// scheduler.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return done != 0;
+}
+
 // Non-blocking probe of a phase.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
@@ -119,7 +143,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, kWaitSuspendNs)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
