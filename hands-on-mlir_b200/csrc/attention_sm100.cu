@@ -118,8 +118,12 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   const int col_k = hidden + head * kHeadDim;
   const int col_v = 2 * hidden + head * kHeadDim;
 
-  uint32_t armed_k = 0, armed_v = 0;  // thread 0 only
-  if (tid == 0) {
+  // Warp 0 runs the copy / MMA issue code as a whole (addresses and descriptors stay
+  // warp-uniform); one elected lane executes the asynchronous instructions.
+  const bool leader = warp == 0 && elect_one();
+  uint32_t armed_k = 0, armed_v = 0;  // counted by every lane of warp 0, used by thread 0
+  if (warp == 0) armed_k = armed_v = 1;
+  if (leader) {
     prefetch_tensormap(&tmQKV);
     mbar_arrive_expect_tx(bar_q, kTileBytes);
     tma_load_2d(smem_base + kSmemQ, &tmQKV, bar_q, col_q, row_base + q0);
@@ -127,7 +131,6 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
     tma_load_2d(smem_base + kSmemK, &tmQKV, bar_k, col_k, row_base);
     mbar_arrive_expect_tx(bar_v, kTileBytes);
     tma_load_2d(smem_base + kSmemV, &tmQKV, bar_v, col_v, row_base);
-    armed_k = armed_v = 1;
   }
 
   constexpr uint32_t idesc_s = make_idesc_f16(kTile, kTile, false, false);
@@ -142,28 +145,30 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   for (int j = 0; j < n_kv && ok; ++j) {
     const uint32_t ph = j & 1;
     // ---- S = Q.K_j^T
-    if (tid == 0) {
+    if (warp == 0) {
       bool w = true;
       if (j == 0) w = mbar_wait(bar_q, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
       w = w && mbar_wait(bar_k, ph, abort_flag, p.status, kDevWaitTimeoutAttention);
-      if (w) {
+      if (__all_sync(0xffffffffu, w)) {
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < kHeadDim / 16; ++k) {
           const uint64_t da = make_smem_desc_sw128(smem_base + kSmemQ + k * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_base + kSmemK + k * 32, 16, 1024);
-          tc_mma_f16_ss(tmem_s, da, db, idesc_s, k != 0 ? 1u : 0u);
+          if (leader) tc_mma_f16_ss(tmem_s, da, db, idesc_s, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar_s);
+        if (leader) tc_commit(bar_s);
       }
     }
     ok = mbar_wait(bar_s, ph, abort_flag, p.status, kDevWaitTimeoutAttention);
     ok = __syncthreads_and(ok);
     if (!ok) break;
     tc_fence_after_sync();
-    if (tid == 0 && j + 1 < n_kv) {  // K buffer is free once S has been computed
-      mbar_arrive_expect_tx(bar_k, kTileBytes);
-      tma_load_2d(smem_base + kSmemK, &tmQKV, bar_k, col_k, row_base + (j + 1) * kTile);
+    if (warp == 0 && j + 1 < n_kv) {  // K buffer is free once S has been computed
+      if (leader) {
+        mbar_arrive_expect_tx(bar_k, kTileBytes);
+        tma_load_2d(smem_base + kSmemK, &tmQKV, bar_k, col_k, row_base + (j + 1) * kTile);
+      }
       ++armed_k;
     }
 
@@ -223,8 +228,8 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
     __syncthreads();
 
     // ---- O_j = P.V_j
-    if (tid == 0) {
-      if (mbar_wait(bar_v, ph, abort_flag, p.status, kDevWaitTimeoutAttention)) {
+    if (warp == 0) {
+      if (__all_sync(0xffffffffu, mbar_wait(bar_v, ph, abort_flag, p.status, kDevWaitTimeoutAttention))) {
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < kTile / 16; ++k) {
@@ -232,18 +237,20 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
               smem_base + kSmemP + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
           // V tile: 128 kv rows of 128 B; N (= d) contiguous, 16 kv rows = 2048 B.
           const uint64_t db = make_smem_desc_sw128(smem_base + kSmemV + k * 2048, kTileBytes, 1024);
-          tc_mma_f16_ss(tmem_o, da, db, idesc_o, k != 0 ? 1u : 0u);
+          if (leader) tc_mma_f16_ss(tmem_o, da, db, idesc_o, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar_o);
+        if (leader) tc_commit(bar_o);
       }
     }
     ok = mbar_wait(bar_o, ph, abort_flag, p.status, kDevWaitTimeoutAttention);
     ok = __syncthreads_and(ok);
     if (!ok) break;
     tc_fence_after_sync();
-    if (tid == 0 && j + 1 < n_kv) {  // V buffer is free once P.V has been computed
-      mbar_arrive_expect_tx(bar_v, kTileBytes);
-      tma_load_2d(smem_base + kSmemV, &tmQKV, bar_v, col_v, row_base + (j + 1) * kTile);
+    if (warp == 0 && j + 1 < n_kv) {  // V buffer is free once P.V has been computed
+      if (leader) {
+        mbar_arrive_expect_tx(bar_v, kTileBytes);
+        tma_load_2d(smem_base + kSmemV, &tmQKV, bar_v, col_v, row_base + (j + 1) * kTile);
+      }
       ++armed_v;
     }
 #pragma unroll
@@ -383,7 +390,10 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   pdl_wait();  // cu_seqlens and the packed QKV come from earlier kernels of the stream
   stamp(1);
   // The tiles do not depend on the valid length: request them before reading it.
-  if (tid == 0) {
+  // Warp 0 runs the copy / MMA issue code as a whole (addresses and descriptors stay
+  // warp-uniform); one elected lane executes the asynchronous instructions.
+  const bool leader = warp == 0 && elect_one();
+  if (leader) {
     const int row_base = batch * p.seq;
     mbar_arrive_expect_tx(bar_load, 3 * kTileBytes);
     tma_load_2d(smem_q, &tmQKV, bar_load, head * kHeadDim, row_base);
@@ -397,8 +407,8 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   bool ok = true;
   float inv = 0.f;
   if (len > 0) {
-    if (tid == 0) {
-      if (mbar_wait(bar_load, 0, abort_flag, p.status, kDevWaitTimeoutAttention)) {
+    if (warp == 0) {
+      if (__all_sync(0xffffffffu, mbar_wait(bar_load, 0, abort_flag, p.status, kDevWaitTimeoutAttention))) {
         stamp(3);
         tc_fence_after_sync();
         constexpr uint32_t idesc_s = make_idesc_f16(kTile, kTile, false, false);
@@ -406,9 +416,9 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
         for (int k = 0; k < kHeadDim / 16; ++k) {
           const uint64_t da = make_smem_desc_sw128(smem_q + k * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_k + k * 32, 16, 1024);
-          tc_mma_f16_ss(tmem_acc, da, db, idesc_s, k != 0 ? 1u : 0u);
+          if (leader) tc_mma_f16_ss(tmem_acc, da, db, idesc_s, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar_s);
+        if (leader) tc_commit(bar_s);
       }
     }
     ok = mbar_wait(bar_s, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
@@ -493,7 +503,7 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
       stamp(6);
       const float l_row = l_part + xchg_sum[(hf ^ 1) * kTile + row];
       inv = (row_live && l_row > 0.f) ? 1.f / l_row : 0.f;
-      if (tid == 0) {
+      if (warp == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc_o = make_idesc_f16(kTile, kHeadDim, false, true);
         const int k_steps = (len + 15) >> 4;  // key groups beyond the last valid key hold no P
@@ -501,9 +511,9 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
           const uint64_t da =
               make_smem_desc_sw128(smem_p + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_v + k * 2048, kTileBytes, 1024);
-          tc_mma_f16_ss(tmem_acc, da, db, idesc_o, k != 0 ? 1u : 0u);
+          if (leader) tc_mma_f16_ss(tmem_acc, da, db, idesc_o, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar_o);
+        if (leader) tc_commit(bar_o);
       }
       ok = mbar_wait(bar_o, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
       ok = __syncthreads_and(ok);
@@ -550,7 +560,7 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
     tc_fence_before_sync();
     __syncthreads();
     stamp(8);
-    if (tid == 0) {
+    if (leader) {
       asm volatile(
           "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
           :

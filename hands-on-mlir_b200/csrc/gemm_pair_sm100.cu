@@ -53,6 +53,7 @@ struct PairParams {
   int b_grouped;  // B [K,N] is fetched through the grouped 3-D tensor map (N % 64 == 0)
   int *status;
   long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
+  long long *tl;    // optional launch-timeline slot (diagnostics), else null
   int dbg;          // profile-mode experiments (HOM_GEMM_DBG): 1 no barrier probe, 2 epilogue only
                     // releases the accumulator, 4 no loads / no stage hand-offs (MMA issue alone),
                     // 8 no per-block tcgen05 fence; results are garbage with 2 and 4
@@ -89,6 +90,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int num_pairs = gridDim.x >> 1;
 
   pdl_launch_dependents();
+  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -156,6 +158,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
       }
       pdl_wait();
+      if (p.tl && leader) timeline_stamp(p.tl, 2);
       for (int tile = pair; tile < p.num_tiles && ok && !(p.dbg & 4); tile += num_pairs) {
         const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
         const int nb0 = (tile % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
@@ -305,6 +308,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
   }
+  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 4);
 }
 
 template <int BN2, bool B_NK>
@@ -396,6 +400,7 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   }
   p.status = device_status_word();
   p.prof = profile_buffer();
+  p.tl = launch_timeline_slot();
   p.dbg = 0;
   if (p.prof) {
     if (const char *env = std::getenv("HOM_GEMM_DBG")) p.dbg = std::atoi(env);

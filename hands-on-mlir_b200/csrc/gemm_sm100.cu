@@ -62,6 +62,7 @@ struct Params {
   int b_grouped;  // B [K,N] is fetched through the grouped 3-D tensor map (N % 64 == 0)
   int *status;
   long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
+  long long *tl;    // optional launch-timeline slot (diagnostics), else null
 };
 
 // Wait that ignores the CTA abort flag; used only to let in-flight TMA land before exit.
@@ -102,6 +103,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   unsigned long long g_entry = 0;
   if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
   pdl_launch_dependents();
+  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -163,6 +165,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       pdl_wait();
+      if (p.tl && leader) timeline_stamp(p.tl, 2);
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / p.n_blocks) * BM;
         const int n0 = (tile % p.n_blocks) * BN;
@@ -306,6 +309,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 4);
   if (p.prof && blockIdx.x == 0 && threadIdx.x == 32) {
     unsigned long long g_exit;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_exit));
@@ -380,14 +384,29 @@ long long *profile_buffer() {
         long long init[32];
         for (int i = 0; i < 32; ++i) init[i] = (i & 1) == 0 ? 0x7fffffffffffffffLL : 0;
         cudaMemcpy(g_profile_buf + 32, init, sizeof(init), cudaMemcpyHostToDevice);
+        // slots [3800, 4088): {first, last} x {entry, dependency resolved, exit} of 48 GEMM launches
+        long long init2[288];
+        for (int i = 0; i < 288; ++i) init2[i] = (i & 1) == 0 ? 0x7fffffffffffffffLL : 0;
+        cudaMemcpy(g_profile_buf + 3800, init2, sizeof(init2), cudaMemcpyHostToDevice);
       }
     }
   }
-  if (g_profile_buf && !std::getenv("HOM_GEMM_TIMELINE")) cudaMemset(g_profile_buf, 0, 15 * sizeof(long long));
+  // The role counters are only collected while one of the variables is (still) set, so that a
+  // program can switch them off before it captures a graph.
+  if (!g_profile_buf || !(std::getenv("HOM_GEMM_PROFILE") || std::getenv("HOM_ATTN_PROFILE"))) return nullptr;
+  if (!std::getenv("HOM_GEMM_TIMELINE")) cudaMemset(g_profile_buf, 0, 15 * sizeof(long long));
   return g_profile_buf;
 }
 
 long long *profile_buffer_raw() { return g_profile_buf; }
+
+// Launch timeline (HOM_GEMM_LAUNCH_TIMELINE set while the calls are made, e.g. during graph
+// capture): the slot this launch stamps, or null.
+long long *launch_timeline_slot() {
+  static int calls = 0;
+  if (!g_profile_buf || !std::getenv("HOM_GEMM_LAUNCH_TIMELINE")) return nullptr;
+  return g_profile_buf + 3800 + 6 * (calls++ % 48);
+}
 
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream) {
   if (std::getenv("HOM_GEMM_TIMELINE")) return;  // stamps are read back by the caller
@@ -538,6 +557,7 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
   }
   p.status = device_status_word();
   p.prof = profile_buffer();
+  p.tl = launch_timeline_slot();
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   const double flops = 2.0 * pb.M * pb.N * pb.K;
   const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
@@ -672,6 +692,7 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
   p.stages = Cfg::kStages;
   p.status = device_status_word_if_ready();
   p.prof = nullptr;
+  p.tl = nullptr;
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
   const double flops = 2.0 * pb.M * pb.N * pb.K;
   const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +

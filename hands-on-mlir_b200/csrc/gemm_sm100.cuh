@@ -50,6 +50,7 @@ int tune_cache_save(const char *path);  // entries written, or -1
 
 long long *profile_buffer();
 long long *profile_buffer_raw();  // the buffer if it exists; touches nothing
+long long *launch_timeline_slot();  // diagnostics: where this launch stamps its CTA entry/exit times
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream);
 
 // Cached cuTensorMapEncodeTiled for a 2-D fp16 tensor [outer, inner], 128-byte swizzle.

@@ -49,6 +49,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Diagnostics: folds the wall clock into {first, last} slots (slot[which], slot[which + 1]).
+__device__ __forceinline__ void timeline_stamp(long long *slot, int which) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  atomicMin(slot + which, static_cast<long long>(t));
+  atomicMax(slot + which + 1, static_cast<long long>(t));
+}
+
 // ------------------------------------------- programmatic dependent launch
 // Kernels are launched with programmatic stream serialization: the next kernel in the stream
 // may start (and run its set-up) while this one is still finishing.  A kernel calls
