@@ -29,14 +29,14 @@ namespace {
 
 constexpr int kTile = 128;   // query rows per CTA and KV rows per step
 constexpr int kHeadDim = 64;
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;  // two threads per query row
 constexpr uint32_t kTileBytes = kTile * kHeadDim * 2;  // 16 KB
 constexpr uint32_t kSmemQ = 0;
 constexpr uint32_t kSmemK = kTileBytes;
 constexpr uint32_t kSmemV = 2 * kTileBytes;
 constexpr uint32_t kSmemP = 3 * kTileBytes;  // two 128 x 64 sub-tiles
 constexpr uint32_t kSmemBar = 5 * kTileBytes;
-constexpr uint32_t kSmemBytes = kSmemBar + 64 + 1024;
+constexpr uint32_t kSmemBytes = kSmemBar + 64 + 2 * kTile * 4 + 1024;  // + row max / sum exchange
 constexpr uint32_t kTmemCols = 256;  // S: columns [0,128), O: columns [128,192)
 
 struct Params {
@@ -55,6 +55,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Any sequence length: online softmax over 128-key tiles.  A query row is shared by threads
+// `row` and `row + 128`: each owns 64 of a tile's 128 key columns (one 128-byte P sub-tile
+// row) and 32 of the 64 output columns, whose running sum lives in its registers.
 __global__ void __launch_bounds__(kThreads, 2)
 attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -65,6 +74,8 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int row = tid & (kTile - 1);
+  const int hf = tid >> 7;
   const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
   const int hidden = p.heads * kHeadDim;
   const int q0 = q_tile * kTile;
@@ -73,15 +84,15 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   int len = p.cu_seqlens[batch + 1] - p.cu_seqlens[batch];
   len = max(0, min(len, p.seq));
 
-  const int q_idx = q0 + tid;
-  __half *out_row = p.out + (static_cast<long long>(batch) * p.seq + q_idx) * hidden + head * kHeadDim;
+  const int q_idx = q0 + row;
+  __half *out_seg = p.out + (static_cast<long long>(batch) * p.seq + q_idx) * hidden + head * kHeadDim + hf * 32;
 
   if (q0 >= len) {
     // Entirely padded query tile.
     if (q_idx < p.seq) {
       const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int g = 0; g < 8; ++g) reinterpret_cast<uint4 *>(out_row)[g] = z;
+      for (int g = 0; g < 4; ++g) reinterpret_cast<uint4 *>(out_seg)[g] = z;
     }
     return;
   }
@@ -90,6 +101,7 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   const uint32_t bar_k = bar_q + 8, bar_v = bar_q + 16, bar_s = bar_q + 24, bar_o = bar_q + 32;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + 40);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float *xchg = reinterpret_cast<float *>(smem_gen + kSmemBar + 64);  // [2][128] row maxima / sums
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -110,7 +122,7 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + 128;
-  const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
 
   const int n_kv = (len + kTile - 1) / kTile;
   const int row_base = batch * p.seq;
@@ -136,10 +148,11 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   constexpr uint32_t idesc_s = make_idesc_f16(kTile, kTile, false, false);
   constexpr uint32_t idesc_o = make_idesc_f16(kTile, kHeadDim, false, true);
 
-  float m_run = -INFINITY, l_run = 0.f;
-  float o_acc[kHeadDim];
+  const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+  float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's half of the row sum
+  float2 o_acc[16];                      // output columns [32 * hf, +32)
 #pragma unroll
-  for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
+  for (int i = 0; i < 16; ++i) o_acc[i] = make_float2(0.f, 0.f);
 
   bool ok = true;
   for (int j = 0; j < n_kv && ok; ++j) {
@@ -172,67 +185,80 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
       ++armed_k;
     }
 
-    // ---- softmax over this KV tile (one query row per thread)
+    // ---- softmax over this KV tile; columns [0, valid) are real keys
     const int kv0 = j * kTile;
-    const int valid = min(kTile, len - kv0);  // columns [0, valid) are real keys
-    float m_tile = -INFINITY;
+    const int valid = min(kTile, len - kv0);
+    float m_part = -INFINITY;
 #pragma unroll 1
-    for (int c = 0; c < kTile / 32; ++c) {
+    for (int c = 2 * hf; c < 2 * hf + 2 && c * 32 < valid; ++c) {
       uint32_t r[32];
       tmem_ld_32x32(tmem_s + lane_sel + c * 32, r);
       tmem_ld_wait();
+      if ((c + 1) * 32 <= valid) {
+        float m0 = m_part, m1 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (c * 32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(r[i]) * p.scale_log2);
-    }
-    const float m_new = fmaxf(m_run, m_tile);
-    const float corr = exp2f(m_run - m_new);  // 0 on the first tile (m_run = -inf)
-    float l_tile = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < kTile / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem_s + lane_sel + c * 32, r);
-      tmem_ld_wait();
-      float pv[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float e = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_new));
-        pv[i] = (c * 32 + i < valid) ? e : 0.f;
-        l_tile += pv[i];
-      }
-      // P[row = tid][c*32 .. c*32+31] as fp16 into the K-major 128B-swizzled sub-tile.
-      const uint32_t sub = smem_base + kSmemP + (c >> 1) * kTileBytes + tid * 128;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const uint32_t chunk = (c & 1) * 4 + g;
-        uint32_t w0, w1, w2, w3;
-        {
-          __half2 h;
-          h = __floats2half2_rn(pv[g * 8 + 0], pv[g * 8 + 1]);
-          w0 = *reinterpret_cast<uint32_t *>(&h);
-          h = __floats2half2_rn(pv[g * 8 + 2], pv[g * 8 + 3]);
-          w1 = *reinterpret_cast<uint32_t *>(&h);
-          h = __floats2half2_rn(pv[g * 8 + 4], pv[g * 8 + 5]);
-          w2 = *reinterpret_cast<uint32_t *>(&h);
-          h = __floats2half2_rn(pv[g * 8 + 6], pv[g * 8 + 7]);
-          w3 = *reinterpret_cast<uint32_t *>(&h);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 x = __fmul2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2);
+          m0 = fmaxf(m0, x.x);
+          m1 = fmaxf(m1, x.y);
         }
-        const uint32_t addr = sub + ((chunk ^ (tid & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
-                     "r"(w2), "r"(w3)
-                     : "memory");
+        m_part = fmaxf(m0, m1);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < valid) m_part = fmaxf(m_part, __uint_as_float(r[i]) * p.scale_log2);
       }
     }
+    xchg[hf * kTile + row] = m_part;
+    __syncthreads();
+    const float m_new = fmaxf(m_run, fmaxf(m_part, xchg[(hf ^ 1) * kTile + row]));
+    const float corr = ex2_approx(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+    float2 l2 = make_float2(0.f, 0.f);
+    {
+      const float2 neg_m2 = make_float2(-m_new, -m_new);
+      const uint32_t sub = smem_base + kSmemP + hf * kTileBytes + row * 128;
+#pragma unroll 1
+      for (int c = 2 * hf; c < 2 * hf + 2 && c * 32 < valid; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_sel + c * 32, r);
+        tmem_ld_wait();
+        const bool full = (c + 1) * 32 <= valid;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int i0 = g * 8 + 2 * jj;
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i0]), __uint_as_float(r[i0 + 1])),
+                                        scale2, neg_m2);
+            float2 e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            if (!full) {
+              e.x = (c * 32 + i0 < valid) ? e.x : 0.f;
+              e.y = (c * 32 + i0 + 1 < valid) ? e.y : 0.f;
+            }
+            l2 = __fadd2_rn(l2, e);
+            const __half2 h = __floats2half2_rn(e.x, e.y);
+            w[jj] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+          const uint32_t chunk = (c & 1) * 4 + g;
+          const uint32_t addr = sub + ((chunk ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                       "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+    }
+    l_run = fmaf(l_run, corr, l2.x + l2.y);
     fence_proxy_async_smem();
     tc_fence_before_sync();
-    __syncthreads();
+    __syncthreads();  // P complete, and every thread is done reading S
 
-    // ---- O_j = P.V_j
+    // ---- O_j = P.V_j over the key groups that hold a valid key
     if (warp == 0) {
       if (__all_sync(0xffffffffu, mbar_wait(bar_v, ph, abort_flag, p.status, kDevWaitTimeoutAttention))) {
         tc_fence_after_sync();
-#pragma unroll
-        for (int k = 0; k < kTile / 16; ++k) {
+        const int k_steps = (valid + 15) >> 4;
+        for (int k = 0; k < k_steps; ++k) {
           const uint64_t da = make_smem_desc_sw128(
               smem_base + kSmemP + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
           // V tile: 128 kv rows of 128 B; N (= d) contiguous, 16 kv rows = 2048 B.
@@ -253,33 +279,39 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
       }
       ++armed_v;
     }
-#pragma unroll
-    for (int c = 0; c < kHeadDim / 32; ++c) {
+    {
       uint32_t r[32];
-      tmem_ld_32x32(tmem_o + lane_sel + c * 32, r);
+      tmem_ld_32x32(tmem_o + lane_sel + hf * 32, r);
       tmem_ld_wait();
+      const float2 corr2 = make_float2(corr, corr);
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], corr, __uint_as_float(r[i]));
+      for (int i = 0; i < 16; ++i)
+        o_acc[i] = __ffma2_rn(o_acc[i], corr2,
+                              make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
     }
-    l_run = fmaf(l_run, corr, l_tile);
     m_run = m_new;
   }
 
   if (ok) {
+    xchg[hf * kTile + row] = l_run;
+    __syncthreads();
+    const float l_row = l_run + xchg[(hf ^ 1) * kTile + row];
     if (q_idx < p.seq) {
-      const bool real_row = q_idx < len && l_run > 0.f;
-      const float inv = real_row ? 1.f / l_run : 0.f;
+      const bool real_row = q_idx < len && l_row > 0.f;
+      const float inv = real_row ? 1.f / l_row : 0.f;
+      const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+      for (int g = 0; g < 4; ++g) {
         uint4 o = make_uint4(0, 0, 0, 0);
         if (real_row) {
           __half2 *o2 = reinterpret_cast<__half2 *>(&o);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            o2[jj] = __floats2half2_rn(o_acc[g * 8 + 2 * jj] * inv, o_acc[g * 8 + 2 * jj + 1] * inv);
+          for (int jj = 0; jj < 4; ++jj) {
+            const float2 v = __fmul2_rn(o_acc[g * 4 + jj], inv2);
+            o2[jj] = __floats2half2_rn(v.x, v.y);
+          }
         }
-        reinterpret_cast<uint4 *>(out_row)[g] = o;
+        reinterpret_cast<uint4 *>(out_seg)[g] = o;
       }
     }
   } else if (tid == 0) {
@@ -308,12 +340,6 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
 constexpr int kThreads1 = 256;  // two threads per query row
 constexpr uint32_t kXchgBytes = 2 * 2 * kTile * 4;  // row maxima and row sums of both halves
 constexpr uint32_t kSmemBytes1 = 3 * kTileBytes + 64 + kXchgBytes + 1024;
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 // A query row is shared by threads `row` and `row + 128`: each owns 64 of the 128 key
 // columns (one 128-byte P sub-tile row) and 32 of the 64 output columns.  Only the 32-column
