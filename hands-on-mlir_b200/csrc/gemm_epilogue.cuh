@@ -58,23 +58,17 @@ __device__ __forceinline__ float2 gelu_erf_fast2(float2 x) {
   return __ffma2_rn(make_float2(-a.x, -a.y), t, relu);
 }
 
-// Epilogue warps per CTA and the shared-memory staging each of them owns: two
-// [32 rows x 64 fp16 columns] tiles, used alternately so that a TMA store can still be reading
-// one while the warp fills the other.
-constexpr int kEpilogueWarps = 8;
+// Epilogue warps per CTA and the shared-memory staging each of them owns.  Sixteen warps -
+// four per tensor-memory lane quarter, each draining one 64-column group of the tile - put
+// four epilogue warps on every scheduler: the epilogue arithmetic (dependent FMA / SFU chains)
+// is latency-bound with fewer, and the last tile's drain, which nothing overlaps, is one
+// 64-column block per warp instead of two.  Each warp stages its [32 rows x 64 fp16 columns]
+// block in one 128-byte-swizzled tile that a TMA store then writes out.
+constexpr int kEpilogueWarps = 16;
 constexpr uint32_t kEpilogueTileBytes = 32 * 128;
-constexpr uint32_t kEpilogueStageBytes = 2 * kEpilogueTileBytes;
+constexpr uint32_t kEpilogueStageBytes = kEpilogueTileBytes;
 constexpr uint32_t kEpilogueStagingBytes = kEpilogueWarps * kEpilogueStageBytes;
 
-// One warp drains a [32 rows x ncols] block of an accumulator (ncols a multiple of 64, possibly
-// 0): thread `lane` owns output row `row0 + lane`.  Per 64-column step the warp reads the
-// accumulator (two tcgen05.ld issued back to back), applies the epilogue in fp32, writes the
-// fp16 results into one of its two 128-byte-swizzled staging tiles and lets one lane hand
-// the tile to TMA, which writes full 128-byte rows to global memory and clips rows >= M and
-// columns >= N.  `tmem_addr` already selects the warp's lane quarter and the block's first
-// column; `n_stores` counts this warp's stores so far (selects the staging tile).  After the
-// last accumulator read the function calls `release()` (the accumulator may be overwritten)
-// while the stores drain.
 // Requests the residual / bias values of one 64-column row segment (row `row`, columns
 // [c0, c0 + 64)); out-of-range groups come back as zeros.
 __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int row, int c0, uint4 (&cval)[8]) {
@@ -82,9 +76,20 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
   const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
   const bool row_ok = ep.c_mode == 2 || row < ep.M;
   if (ep.unaligned_n) {
-    __half *dst = reinterpret_cast<__half *>(cval);
-#pragma unroll 8
-    for (int i = 0; i < 64; ++i) dst[i] = (row_ok && c0 + i < ep.N) ? cp[i] : __float2half_rn(0.f);
+    // element-wise reads, packed in registers (no addressable array: keeps cval out of local memory)
+    const unsigned short *cu = reinterpret_cast<const unsigned short *>(cp);
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = g * 8 + 2 * j;
+        const uint32_t lo = (row_ok && c0 + i < ep.N) ? cu[i] : 0u;
+        const uint32_t hi = (row_ok && c0 + i + 1 < ep.N) ? cu[i + 1] : 0u;
+        w[j] = lo | (hi << 16);
+      }
+      cval[g] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
     return;
   }
 #pragma unroll
@@ -94,107 +99,109 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
   }
 }
 
-// `cfirst` holds the residual / bias values of the block's first step, requested by the caller
-// (epilogue_load_c) before it waited for the accumulator so that their latency hides behind
-// the main loop; the values of each later step are requested one step ahead.
+// One warp drains a [32 rows x 64 columns] block of an accumulator: thread `lane` owns output
+// row `row0 + lane`.  The block is read from tensor memory in two 32-column halves (keeps the
+// live registers below the 112 a 576-thread CTA allows), the epilogue is applied in fp32, the
+// fp16 results go into the warp's 128-byte-swizzled staging tile and one lane hands the tile to
+// TMA, which writes full 128-byte rows to global memory and clips rows >= M and columns >= N.
+// `tmem_addr` already selects the warp's lane quarter and the block's first column.  `cval`
+// holds the residual / bias values of the block, requested by the caller (epilogue_load_c)
+// before it waited for the accumulator so that their latency hides behind the main loop.
+// After the last accumulator read the function calls `release()` (the accumulator may be
+// overwritten) while the store drains.  A warp whose column group lies outside the tile
+// (`active` false) only releases.
 template <typename Release>
 __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
-                                                    uint32_t tmem_addr, int row0, int col0, int ncols,
-                                                    uint32_t stage_smem, int lane, uint32_t &n_stores,
-                                                    uint4 (&cfirst)[8], Release release) {
+                                                    uint32_t tmem_addr, int row0, int c0, bool active,
+                                                    uint32_t stage_smem, int lane, uint4 (&cval)[8],
+                                                    Release release) {
   using namespace hom::ptx;
-  const int row = row0 + lane;
-  const int steps = ncols / 64;
-  if (steps == 0) {
+  if (!active) {
     tc_fence_before_sync();
     __syncwarp();
     release();
     return;
   }
-#pragma unroll 1
-  for (int step = 0; step < steps; ++step) {
-    const int c0 = col0 + step * 64;
-    const uint32_t tile = stage_smem + (n_stores & 1u) * kEpilogueTileBytes;
-    const uint32_t my_row = tile + lane * 128;
-    uint32_t acc[2][32];
-    tmem_ld_32x32(tmem_addr + step * 64, acc[0]);
-    tmem_ld_32x32(tmem_addr + step * 64 + 32, acc[1]);
-    uint4 cval[8];
+  const int row = row0 + lane;
+  const uint32_t my_row = stage_smem + lane * 128;
+  float rs = 0.f, sh = 0.f;
+  if (ep.row_scale != nullptr && row < ep.M) {
+    rs = __half2float(ep.row_scale[row]);
+    sh = __half2float(ep.row_shift[row]);
+  }
+  const float2 alpha2 = make_float2(ep.alpha, ep.alpha), beta2 = make_float2(ep.beta, ep.beta);
 #pragma unroll
-    for (int g = 0; g < 8; ++g) cval[g] = cfirst[g];
-    if (step + 1 < steps) epilogue_load_c(ep, row, c0 + 64, cfirst);  // next step's values
+  for (int half = 0; half < 2; ++half) {
+    uint32_t acc[32];
+    tmem_ld_32x32(tmem_addr + half * 32, acc);
     tmem_ld_wait();
-    if (step == steps - 1) {
+    if (half == 1) {
       tc_fence_before_sync();
       __syncwarp();
       release();
+    } else {
+      // The staging tile was handed to TMA by this warp's previous block: that read must be over.
+      if (lane == 0) bulk_wait_group_read_0();
+      __syncwarp();
     }
     if (ep.row_scale != nullptr) {
-      const bool row_in = row < ep.M;
-      const float rs = row_in ? __half2float(ep.row_scale[row]) : 0.f;
-      const float sh = row_in ? __half2float(ep.row_shift[row]) : 0.f;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float cs = c0 + i < ep.N ? ep.col_sum[c0 + i] : 0.f;
-        acc[i >> 5][i & 31] = __float_as_uint(fmaf(rs, __uint_as_float(acc[i >> 5][i & 31]), sh * cs));
+      for (int i = 0; i < 32; ++i) {
+        const int col = c0 + half * 32 + i;
+        const float cs = col < ep.N ? ep.col_sum[col] : 0.f;
+        acc[i] = __float_as_uint(fmaf(rs, __uint_as_float(acc[i]), sh * cs));
       }
     }
-    // This staging tile was last handed to TMA two stores ago: that read must be over.
-    if (lane == 0) bulk_wait_group_read_1();
-    __syncwarp();
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      const float2 alpha2 = make_float2(ep.alpha, ep.alpha), beta2 = make_float2(ep.beta, ep.beta);
-      const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[g]);
+    for (int g = 0; g < 4; ++g) {
+      const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[half * 4 + g]);
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int i0 = (g & 3) * 8 + 2 * j;
-        float2 v = __fmul2_rn(alpha2, make_float2(__uint_as_float(acc[g >> 2][i0]),
-                                                  __uint_as_float(acc[g >> 2][i0 + 1])));
+        const int i0 = g * 8 + 2 * j;
+        float2 v = __fmul2_rn(alpha2, make_float2(__uint_as_float(acc[i0]), __uint_as_float(acc[i0 + 1])));
         if (ep.c_mode != 0) v = __ffma2_rn(beta2, __half22float2(h2[j]), v);
         if (ep.act == 1) v = gelu_erf_fast2(v);
         const __half2 h = __floats2half2_rn(v.x, v.y);
         w[j] = *reinterpret_cast<const uint32_t *>(&h);
       }
-      const uint32_t addr = my_row + ((static_cast<uint32_t>(g) ^ (lane & 7u)) << 4);
+      const uint32_t addr = my_row + ((static_cast<uint32_t>(half * 4 + g) ^ (lane & 7u)) << 4);
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
                    "r"(w[2]), "r"(w[3])
                    : "memory");
     }
-    if (!ep.unaligned_n) {
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, tile, c0, row0);
-        bulk_commit_group();  // one group per step (possibly empty) keeps the tile rotation exact
-      }
-    } else {
-      // Rows of D are not 16-byte aligned: the warp copies its staging tile out row by row,
-      // lane l writing columns c0 + 2l, c0 + 2l + 1 (one 128-byte row segment per instruction).
-      __syncwarp();
-      const int col = c0 + 2 * lane;
-      const uint32_t chunk = static_cast<uint32_t>(lane) >> 2, within = (static_cast<uint32_t>(lane) & 3u) << 2;
-      for (int r = 0; r < 32; ++r) {
-        const int grow = row0 + r;
-        if (grow >= ep.M) break;
-        uint32_t word;
-        asm volatile("ld.shared.b32 %0, [%1];"
-                     : "=r"(word)
-                     : "r"(tile + r * 128 + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4) + within)
-                     : "memory");
-        __half *dp = ep.D + static_cast<long long>(grow) * ep.ldd + col;
-        if (col + 1 < ep.N && (reinterpret_cast<uintptr_t>(dp) & 3u) == 0) {
-          *reinterpret_cast<uint32_t *>(dp) = word;
-        } else {
-          const __half2 h = *reinterpret_cast<const __half2 *>(&word);
-          if (col < ep.N) dp[0] = __low2half(h);
-          if (col + 1 < ep.N) dp[1] = __high2half(h);
-        }
-      }
-      __syncwarp();
+  }
+  if (!ep.unaligned_n) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, stage_smem, c0, row0);
+      bulk_commit_group();
     }
-    ++n_stores;
+  } else {
+    // Rows of D are not 16-byte aligned: the warp copies its staging tile out row by row,
+    // lane l writing columns c0 + 2l, c0 + 2l + 1 (one 128-byte row segment per instruction).
+    __syncwarp();
+    const int col = c0 + 2 * lane;
+    const uint32_t chunk = static_cast<uint32_t>(lane) >> 2, within = (static_cast<uint32_t>(lane) & 3u) << 2;
+    for (int r = 0; r < 32; ++r) {
+      const int grow = row0 + r;
+      if (grow >= ep.M) break;
+      uint32_t word;
+      asm volatile("ld.shared.b32 %0, [%1];"
+                   : "=r"(word)
+                   : "r"(stage_smem + r * 128 + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4) + within)
+                   : "memory");
+      __half *dp = ep.D + static_cast<long long>(grow) * ep.ldd + col;
+      if (col + 1 < ep.N && (reinterpret_cast<uintptr_t>(dp) & 3u) == 0) {
+        *reinterpret_cast<uint32_t *>(dp) = word;
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2 *>(&word);
+        if (col < ep.N) dp[0] = __low2half(h);
+        if (col + 1 < ep.N) dp[1] = __high2half(h);
+      }
+    }
+    __syncwarp();
   }
 }
 

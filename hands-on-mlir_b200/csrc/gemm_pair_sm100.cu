@@ -30,7 +30,7 @@ using namespace hom::ptx;
 namespace {
 
 constexpr int BK = 64;
-constexpr int kPairThreads = 320;
+constexpr int kPairThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kABytes = 128 * BK * 2;
 
 template <int BN2>
@@ -252,46 +252,44 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   } else {
     // --------------------------------------------------------------- epilogue
-    const int quarter = warp & 3;          // tensor-memory lanes [32*quarter, +32)
-    const int col_half = (warp - 2) >> 2;  // which half of the tile's columns
+    const int quarter = warp & 3;       // tensor-memory lanes [32*quarter, +32)
+    const int group = (warp - 2) >> 2;  // which 64-column group of the tile
+    const int col_begin = group * 64;
+    const bool active = col_begin < BN2;
     const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
     int it = 0;
-    uint32_t n_stores = 0;
     long long t_wait = 0, t_begin = clock64();
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
-      const int n0 = (tile % p.n_blocks) * BN2 + col_half * HALF;
-      uint4 cfirst[8];
-      epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cfirst);
+      const int n0 = (tile % p.n_blocks) * BN2 + col_begin;
+      uint4 cval[8];
+      if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cval);
       const long long tw = p.prof ? clock64() : 0;
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (p.prof) t_wait += clock64() - tw;
       tc_fence_after_sync();
+      auto release = [&]() {
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(tempty_bar(acc));
+          else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+        }
+      };
       if (p.dbg & 2) {
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) {
-          if (rank == 0) mbar_arrive(tempty_bar(acc));
-          else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
-        }
+        release();
         continue;
       }
       const uint32_t t_row =
-          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_half * HALF;
-      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, HALF, stage_smem, lane, n_stores,
-                          cfirst, [&]() {
-        if (lane == 0) {
-          if (rank == 0) mbar_arrive(tempty_bar(acc));
-          else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
-        }
-      });
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_begin;
+      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, active, stage_smem, lane, cval, release);
     }
-    // Stores still in flight read this warp's staging tile: let them finish reading it.
+    // A store still in flight reads this warp's staging tile: let it finish reading.
     if (lane == 0) bulk_wait_group_read_0();
     __syncwarp();
     if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {

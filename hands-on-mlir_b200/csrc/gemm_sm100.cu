@@ -45,9 +45,6 @@ struct TileCfg {
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   // As many stages as fit beside the 64 KB of epilogue staging.
   static constexpr int kStages = BN == 256 ? 3 : BN == 192 ? 4 : BN == 128 ? 5 : 6;
-  // Columns drained by the first / second group of four epilogue warps (multiples of 64).
-  static constexpr int kCols0 = BN == 64 ? 64 : BN == 192 ? 128 : BN / 2;
-  static constexpr int kCols1 = BN - kCols0;
   static constexpr uint32_t kTmemCols = BN == 64 ? 128 : BN == 128 ? 256 : 512;
   static constexpr uint32_t kStagingBytes = kEpilogueStagingBytes;
   static constexpr uint32_t kBarrierBytes = 8 * (2 * kStages + 4) + 16;
@@ -265,12 +262,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else {
     // --------------------------------------------------------------- epilogue
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
-    const int group = (warp - 2) >> 2;  // first or second group of columns
-    const int col_begin = group == 0 ? 0 : Cfg::kCols0;
-    const int ncols = group == 0 ? Cfg::kCols0 : Cfg::kCols1;
+    const int quarter = warp & 3;       // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int group = (warp - 2) >> 2;  // which 64-column group of the tile
+    const int col_begin = group * 64;
+    const bool active = col_begin < BN;
     const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
-    uint32_t n_stores = 0;
     int it = 0;
     long long t_wait = 0, t_begin = clock64();
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
@@ -279,8 +275,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const uint32_t acc_ph = (it >> 1) & 1;
       const int m0 = (tile / p.n_blocks) * BM;
       const int n0 = (tile % p.n_blocks) * BN;
-      uint4 cfirst[8];
-      if (ncols > 0) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cfirst);
+      uint4 cval[8];
+      if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
       const long long tw = p.prof ? clock64() : 0;
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
@@ -289,12 +285,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_after_sync();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + col_begin;
-      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, ncols, stage_smem, lane,
-                          n_stores, cfirst, [&]() {
+      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem, lane,
+                          cval, [&]() {
                             if (lane == 0) mbar_arrive(tempty_bar(acc));
                           });
     }
-    // Stores still in flight read this warp's staging tile: let them finish reading it.
+    // A store still in flight reads this warp's staging tile: let it finish reading.
     if (lane == 0) bulk_wait_group_read_0();
     __syncwarp();
     if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {
