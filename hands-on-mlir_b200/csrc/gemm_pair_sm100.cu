@@ -54,9 +54,6 @@ struct PairParams {
   int *status;
   long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
   long long *tl;    // optional launch-timeline slot (diagnostics), else null
-  int dbg;          // profile-mode experiments (HOM_GEMM_DBG): 1 no barrier probe, 2 epilogue only
-                    // releases the accumulator, 4 no loads / no stage hand-offs (MMA issue alone),
-                    // 8 no per-block tcgen05 fence; results are garbage with 2 and 4
 };
 
 template <int BN2, bool B_NK>
@@ -149,7 +146,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       // B holds weights, which no earlier kernel of the stream writes: the first ring of B
       // tiles is requested before waiting for the previous kernel, A only after.
       int pre = 0;
-      if (pair < p.num_tiles && !(p.dbg & 4)) {
+      if (pair < p.num_tiles) {
         const int nb0 = (pair % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
         pre = p.num_kb < stages_used ? p.num_kb : stages_used;
         for (int kb = 0; kb < pre; ++kb) {
@@ -159,7 +156,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       }
       pdl_wait();
       if (p.tl && leader) timeline_stamp(p.tl, 2);
-      for (int tile = pair; tile < p.num_tiles && ok && !(p.dbg & 4); tile += num_pairs) {
+      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
         const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
         const int nb0 = (tile % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
         for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -215,7 +212,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const uint32_t d_tmem = tmem_base + acc * BN2;
         bool have = false;  // full[s] already seen complete by the probe of the previous block
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!have && !(p.dbg & 4)) {
+          if (!have) {
             const long long tw = p.prof ? clock64() : 0;
             ok = __all_sync(0xffffffffu,
                             mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma));
@@ -223,7 +220,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             if (p.prof) t_full += clock64() - tw;
           }
           have = false;
-          if (!(p.dbg & 8)) tc_fence_after_sync();
+          tc_fence_after_sync();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + kABytes;
           const int s_next = s + 1 == stages_used ? 0 : s + 1;
@@ -235,10 +232,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                      : make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024);
             if (leader) tc_mma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             // Probe the next stage while the tensor pipe is busy with what was just queued.
-            if (k == 1 && kb + 1 < p.num_kb && !(p.dbg & 5))
+            if (k == 1 && kb + 1 < p.num_kb)
               have = __all_sync(0xffffffffu, mbar_test_wait(full_bar(s_next), ph_next));
           }
-          if (leader && !(p.dbg & 4)) tc_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
+          if (leader) tc_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
           s = s_next;
           ph = ph_next;
         }
@@ -279,12 +276,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
         }
       };
-      if (p.dbg & 2) {
-        tc_fence_before_sync();
-        __syncwarp();
-        release();
-        continue;
-      }
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_begin;
       epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, active, stage_smem, lane, cval, release);
@@ -399,10 +390,6 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   p.status = device_status_word();
   p.prof = profile_buffer();
   p.tl = launch_timeline_slot();
-  p.dbg = 0;
-  if (p.prof) {
-    if (const char *env = std::getenv("HOM_GEMM_DBG")) p.dbg = std::atoi(env);
-  }
   const int pairs = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
   cfg.gridDim = dim3(2 * pairs);
   const double flops = 2.0 * pb.M * pb.N * pb.K;
