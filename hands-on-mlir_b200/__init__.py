@@ -141,6 +141,7 @@ _SIGNATURES = {
     "homKernelLaunchCount": (c_int64, []),
     "homOpTimingEnable": (None, [ctypes.c_int]),
     "homOpTimingCollect": (c_int64, [ctypes.POINTER(OpTiming), c_int64]),
+    "homOpTimingPeek": (c_int64, [ctypes.POINTER(OpTiming), c_int64]),
     "homGemmQueryTile": (c_int32, [c_int64, c_int64, c_int64, c_int64,
                                    ctypes.POINTER(c_int32), ctypes.POINTER(c_int32),
                                    ctypes.POINTER(c_int32)]),
@@ -314,6 +315,12 @@ class RunnerUtils:
     def collect_op_timings(self, capacity: int = 1 << 16):
         buf = (OpTiming * capacity)()
         n = int(self.lib.homOpTimingCollect(buf, capacity))
+        return [(buf[i].kind, buf[i].ms, buf[i].flops, buf[i].bytes) for i in range(min(n, capacity))]
+
+    def peek_op_timings(self, capacity: int = 1 << 16):
+        """Durations of the recorded launches without releasing them (graph replays re-record)."""
+        buf = (OpTiming * capacity)()
+        n = int(self.lib.homOpTimingPeek(buf, capacity))
         return [(buf[i].kind, buf[i].ms, buf[i].flops, buf[i].bytes) for i in range(min(n, capacity))]
 
     def gemm_query_tile(self, m, n, k, activation=0):

@@ -97,6 +97,18 @@ int sm_count() {
   return n > 0 ? n : 148;
 }
 
+namespace {
+// Inside stream capture a plain cudaEventRecord only expresses a dependency; the external flag
+// turns it into an event-record node that is re-recorded by every replay and can be timed.
+void record_event(cudaEvent_t ev, cudaStream_t stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) == cudaSuccess && st == cudaStreamCaptureStatusActive)
+    cudaEventRecordWithFlags(ev, stream, cudaEventRecordExternal);
+  else
+    cudaEventRecord(ev, stream);
+}
+}  // namespace
+
 LaunchScope::LaunchScope(OpKind kind, double flops, double bytes) {
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   if (!g_timing_enabled.load(std::memory_order_relaxed)) return;
@@ -106,7 +118,7 @@ LaunchScope::LaunchScope(OpKind kind, double flops, double bytes) {
     cudaEventDestroy(rec.start);
     return;
   }
-  cudaEventRecord(rec.start, current_stream());
+  record_event(rec.start, current_stream());
   std::lock_guard<std::mutex> lock(g_timing_mutex);
   g_timing_log.push_back(rec);
   slot_ = static_cast<int>(g_timing_log.size()) - 1;
@@ -116,7 +128,7 @@ LaunchScope::~LaunchScope() {
   if (slot_ < 0) return;
   std::lock_guard<std::mutex> lock(g_timing_mutex);
   if (slot_ < static_cast<int>(g_timing_log.size()))
-    cudaEventRecord(g_timing_log[slot_].stop, current_stream());
+    record_event(g_timing_log[slot_].stop, current_stream());
 }
 
 }  // namespace hom
@@ -155,6 +167,22 @@ int homSynchronize(void) {
 int64_t homKernelLaunchCount(void) { return hom::g_launch_count.load(); }
 
 void homOpTimingEnable(int enable) { hom::g_timing_enabled.store(enable != 0); }
+
+int64_t homOpTimingPeek(HomOpTiming *out, int64_t capacity) {
+  cudaDeviceSynchronize();
+  std::lock_guard<std::mutex> lock(hom::g_timing_mutex);
+  const int64_t n = static_cast<int64_t>(hom::g_timing_log.size());
+  for (int64_t i = 0; i < n && i < capacity && out; ++i) {
+    auto &rec = hom::g_timing_log[i];
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, rec.start, rec.stop) != cudaSuccess) ms = -1.f;
+    out[i].kind = rec.kind;
+    out[i].ms = ms;
+    out[i].flops = rec.flops;
+    out[i].bytes = rec.bytes;
+  }
+  return n;
+}
 
 int64_t homOpTimingCollect(HomOpTiming *out, int64_t capacity) {
   cudaDeviceSynchronize();

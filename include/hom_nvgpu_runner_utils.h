@@ -244,6 +244,10 @@ typedef struct HomOpTiming {
 } HomOpTiming;
 HOM_EXPORT void homOpTimingEnable(int enable);
 HOM_EXPORT int64_t homOpTimingCollect(HomOpTiming *out, int64_t capacity);
+/* The same read-out without releasing the records: for launches that were captured into a CUDA
+ * graph while timing was enabled (their event records became graph nodes), call it after each
+ * replay; call homOpTimingCollect once the graph is gone. */
+HOM_EXPORT int64_t homOpTimingPeek(HomOpTiming *out, int64_t capacity);
 
 /* The tile the GEMM family would run for (M, N, K, activation): the tile's N extent,
  * pipeline stages and split-K.  Returns the tile-table row number (usable as gemmNum). */
