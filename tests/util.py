@@ -54,3 +54,14 @@ def assert_end_to_end_close(got, want, what=""):
     assert frac <= 1e-3, f"{what}: {frac:.2%} of elements outside rtol/atol 1e-3 (max err {err.max():.3e})"
     loose = (err <= 1e-2) | (err <= 1e-2 * np.abs(want))
     assert loose.all(), f"{what}: max abs err {err.max():.3e} exceeds the 1e-2 end-to-end bound"
+
+
+def drift_fractions(got, want):
+    """Fractions of elements outside rtol/atol 1e-3, outside 2e-3, and outside the reference's
+    own end-to-end bound (abs <= 1e-2 or rel <= 1e-2, examples/torch/bert/bert.cu:148-153)."""
+    got = np.asarray(got).astype(np.float64)
+    want = np.asarray(want).astype(np.float64)
+    assert got.shape == want.shape and np.isfinite(got).all()
+    err, mag = np.abs(got - want), np.abs(want)
+    return (float(np.mean(err > 1e-3 + 1e-3 * mag)), float(np.mean(err > 2e-3 + 2e-3 * mag)),
+            float(np.mean((err > 1e-2) & (err > 1e-2 * mag))))
