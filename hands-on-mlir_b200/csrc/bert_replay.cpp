@@ -64,6 +64,10 @@ struct Program {
   cudaEvent_t slot_done[2] = {nullptr, nullptr};   // slot delivered to the host (copy stream)
   bool slot_busy[2] = {false, false};
   unsigned long long host_steps = 0;
+  // one graph per slot holding the whole host step: three input copies, the call sequence and
+  // the copy of the result into the slot (valid for the host input buffers it was captured on)
+  cudaGraphExec_t host_graph[2] = {nullptr, nullptr};
+  const void *host_graph_in[2][3] = {{nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr}};
   void *graph_ids = nullptr, *graph_mask = nullptr, *graph_types = nullptr;
   bool warmed_up = false;
 };
@@ -80,6 +84,36 @@ void release(Tensor &t, bool f16) {
 }
 
 int status() { return homGetLastError(); }
+
+// Staging kernels of the host entry point.  Copy-engine nodes between kernel nodes cost a
+// hand-over of tens of microseconds each inside a graph; plain kernels do not.
+// Reads the three int64 [batch, seq] planes straight from pinned (device-accessible) host
+// memory.
+__global__ void stage_inputs_kernel(const long long *ids, const long long *mask, const long long *types,
+                                    long long *d_ids, long long *d_mask, long long *d_types, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    d_ids[i] = ids[i];
+    d_mask[i] = mask[i];
+    d_types[i] = types[i];
+  }
+}
+
+__global__ void copy_u4_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
+// The device-side alias of a pinned host buffer, or null for pageable memory.
+const long long *device_alias(const void *host_ptr) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (attr.type != cudaMemoryTypeHost || !attr.devicePointer) return nullptr;
+  return static_cast<const long long *>(attr.devicePointer);
+}
 
 // The straight-line call sequence of `_hom_forward`.
 int issue_forward(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void *mask,
@@ -219,6 +253,8 @@ void homBertDestroy(void *program) {
   auto *p = static_cast<Program *>(program);
   if (!p) return;
   if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
+  for (int i = 0; i < 2; ++i)
+    if (p->host_graph[i]) cudaGraphExecDestroy(p->host_graph[i]);
   if (p->own_stream) cudaStreamDestroy(p->own_stream);
   if (p->copy_stream) {
     cudaStreamSynchronize(p->copy_stream);
@@ -328,18 +364,79 @@ int homBertForwardHostAsync(void *program, const int64_t *ids_host, const int64_
   if (p->slot_busy[slot] && cudaStreamWaitEvent(stream, p->slot_done[slot], 0) != cudaSuccess)
     return HOM_ERR_CUDA;
   const size_t plane = static_cast<size_t>(c.batch) * c.seq * 8;
-  if (cudaMemcpyAsync(p->ids_dev.data(), ids_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
-      cudaMemcpyAsync(p->mask_dev.data(), mask_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
-      cudaMemcpyAsync(p->types_dev.data(), types_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess)
-    return HOM_ERR_CUDA;
-  const int rc = forward_impl(*p, 2, p->ids_dev.desc, 2, p->mask_dev.desc, 2, p->types_dev.desc, use_graph);
-  if (rc != 0) return rc;
   const size_t out_bytes = static_cast<size_t>(c.batch) * c.seq * c.hidden * 2;
-  // The hidden-state buffer is reused by the next forward: park the result in the slot, then
-  // let the copy stream deliver it while the next forward runs.
-  if (cudaMemcpyAsync(p->result_slot[slot].data(), p->x.data(), out_bytes, cudaMemcpyDeviceToDevice,
-                      stream) != cudaSuccess ||
-      cudaEventRecord(p->slot_ready[slot], stream) != cudaSuccess ||
+  // Input copies, the call sequence and the copy that parks the result in the slot (the
+  // hidden-state buffer is reused by the next forward).
+  const long long *ids_alias = device_alias(ids_host), *mask_alias = device_alias(mask_host);
+  const long long *types_alias = device_alias(types_host);
+  const bool pinned_inputs = ids_alias && mask_alias && types_alias;
+  auto issue_step = [&]() -> int {
+    if (pinned_inputs) {
+      const int n = c.batch * c.seq;
+      stage_inputs_kernel<<<(n + 255) / 256 < 64 ? (n + 255) / 256 : 64, 256, 0, stream>>>(
+          ids_alias, mask_alias, types_alias, static_cast<long long *>(p->ids_dev.data()),
+          static_cast<long long *>(p->mask_dev.data()), static_cast<long long *>(p->types_dev.data()), n);
+      if (cudaGetLastError() != cudaSuccess) return HOM_ERR_CUDA;
+    } else {
+      return HOM_ERR_INVALID;
+    }
+    const int rc = issue_forward(*p, 2, p->ids_dev.desc, 2, p->mask_dev.desc, 2, p->types_dev.desc);
+    if (rc != 0) return rc;
+    copy_u4_kernel<<<592, 256, 0, stream>>>(static_cast<const uint4 *>(p->x.data()),
+                                           static_cast<uint4 *>(p->result_slot[slot].data()),
+                                           static_cast<long long>(out_bytes / 16));
+    return cudaGetLastError() == cudaSuccess ? 0 : HOM_ERR_CUDA;
+  };
+  for (const Tensor &w : p->weights)
+    if (!w.desc) return HOM_ERR_INVALID;
+  if (!pinned_inputs) {
+    // Pageable host memory cannot be read by a kernel, and copies from it cannot be captured:
+    // copy eagerly, then the (possibly graph-replayed) call sequence and the slot copy.
+    if (cudaMemcpyAsync(p->ids_dev.data(), ids_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        cudaMemcpyAsync(p->mask_dev.data(), mask_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        cudaMemcpyAsync(p->types_dev.data(), types_host, plane, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+      return HOM_ERR_CUDA;
+    const int rc = forward_impl(*p, 2, p->ids_dev.desc, 2, p->mask_dev.desc, 2, p->types_dev.desc, use_graph);
+    if (rc != 0) return rc;
+    copy_u4_kernel<<<592, 256, 0, static_cast<cudaStream_t>(homGetStream())>>>(
+        static_cast<const uint4 *>(p->x.data()), static_cast<uint4 *>(p->result_slot[slot].data()),
+        static_cast<long long>(out_bytes / 16));
+    if (cudaGetLastError() != cudaSuccess) return HOM_ERR_CUDA;
+  } else if (!use_graph || !p->warmed_up || stream == nullptr) {
+    // eager: also the first call of a program (one-time set-up must not happen during capture)
+    // and the legacy default stream, which cannot be captured
+    p->warmed_up = true;
+    const int rc = issue_step();
+    if (rc != 0) return rc;
+  } else {
+    const void *in[3] = {ids_host, mask_host, types_host};
+    if (p->host_graph[slot] && (in[0] != p->host_graph_in[slot][0] || in[1] != p->host_graph_in[slot][1] ||
+                                in[2] != p->host_graph_in[slot][2])) {
+      cudaGraphExecDestroy(p->host_graph[slot]);
+      p->host_graph[slot] = nullptr;
+    }
+    if (!p->host_graph[slot]) {
+      cudaGraph_t graph = nullptr;
+      if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return HOM_ERR_CUDA;
+      const int rc = issue_step();
+      const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
+      if (rc != 0 || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc ? rc : HOM_ERR_CUDA;
+      }
+      const cudaError_t ie = cudaGraphInstantiate(&p->host_graph[slot], graph, 0);
+      cudaGraphDestroy(graph);
+      if (ie != cudaSuccess) {
+        p->host_graph[slot] = nullptr;
+        return HOM_ERR_CUDA;
+      }
+      for (int i = 0; i < 3; ++i) p->host_graph_in[slot][i] = in[i];
+    }
+    if (cudaGraphLaunch(p->host_graph[slot], stream) != cudaSuccess) return HOM_ERR_CUDA;
+    if (const int rc = status()) return rc;
+  }
+  // Let the copy stream deliver the slot while the next forward runs.
+  if (cudaEventRecord(p->slot_ready[slot], stream) != cudaSuccess ||
       cudaStreamWaitEvent(p->copy_stream, p->slot_ready[slot], 0) != cudaSuccess ||
       cudaMemcpyAsync(out_host, p->result_slot[slot].data(), out_bytes, cudaMemcpyDeviceToHost,
                       p->copy_stream) != cudaSuccess ||

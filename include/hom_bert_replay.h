@@ -77,6 +77,9 @@ HOM_EXPORT int homBertForwardHost(void *program, const int64_t *ids_host, const 
 /* The same step without the final wait: the result is parked in one of two device slots and
  * delivered to out_host by a copy stream while the caller already issues the next step.
  * At most two steps are in flight; out_host buffers of consecutive calls must differ.
+ * With use_graph != 0 (and a stream set with homSetStream: the default stream cannot be
+ * captured) the whole step - input copies, call sequence, copy into the slot - is one CUDA
+ * graph per slot, re-captured when the host input pointers change.
  * homBertWaitHost() waits until every issued step has been delivered. */
 HOM_EXPORT int homBertForwardHostAsync(void *program, const int64_t *ids_host,
                                        const int64_t *mask_host, const int64_t *types_host,

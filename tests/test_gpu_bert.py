@@ -152,6 +152,12 @@ def test_graph_replay_and_host_entry_point_are_bit_identical(hom, cuda, oracle):
     prog.wait_host()
     assert_bits_equal(out_h.numpy(), eager, "async host entry point, slot 0")
     assert_bits_equal(out_h2.numpy(), eager, "async host entry point, slot 1")
+    # pageable host inputs (numpy arrays) take the copy path instead of the staging kernel
+    for i in range(3):
+        out_h.zero_()
+        prog.forward_host_async(ids, mask, types, out_h, use_graph=True)
+        prog.wait_host()
+        assert_bits_equal(out_h.numpy(), eager, "async host entry point, pageable inputs")
     h2d, d2h = prog.host_traffic()
     assert h2d == 3 * B * S * 8 and d2h == B * S * cfg.hidden * 2
     prog.close()
