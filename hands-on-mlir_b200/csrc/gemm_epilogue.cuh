@@ -130,6 +130,7 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
     sh = __half2float(ep.row_shift[row]);
   }
   const float2 alpha2 = make_float2(ep.alpha, ep.alpha), beta2 = make_float2(ep.beta, ep.beta);
+  const bool unit_alpha = ep.alpha == 1.0f;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     uint32_t acc[32];
@@ -159,7 +160,8 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int i0 = g * 8 + 2 * j;
-        float2 v = __fmul2_rn(alpha2, make_float2(__uint_as_float(acc[i0]), __uint_as_float(acc[i0 + 1])));
+        float2 v = make_float2(__uint_as_float(acc[i0]), __uint_as_float(acc[i0 + 1]));
+        if (!unit_alpha) v = __fmul2_rn(alpha2, v);  // alpha * x is exact for alpha == 1: skip it
         if (ep.c_mode != 0) v = __ffma2_rn(beta2, __half22float2(h2[j]), v);
         if (ep.act == 1) v = gelu_erf_fast2(v);
         const __half2 h = __floats2half2_rn(v.x, v.y);
