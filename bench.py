@@ -447,7 +447,8 @@ def run_gpu_arm(args, cfg, workload):
         local_batch, first, global_batch = hi - lo, lo, workload["batch"]
     seq = workload["seq"]
 
-    prog = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding)
+    prog = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding,
+                       fused_layernorm=args.fused_layernorm)
     weights = make_weights_torch(cfg, seq, device)
     prog.set_weights(weights)
     ids_np, mask_np, types_np = make_inputs(workload, local_batch, first)
@@ -509,7 +510,8 @@ def run_gpu_arm(args, cfg, workload):
     # by event-record nodes on the launching stream; the graph is replayed and read out n_prof
     # times.  (The event nodes stand between the kernels, so this pass runs without the
     # programmatic overlap of neighbouring launches that the timed region above has.)
-    prog_t = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding)
+    prog_t = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding,
+                         fused_layernorm=args.fused_layernorm)
     prog_t.set_weights(weights)
     prog_t.forward(ids_d, mask_d, types_d, use_graph=True)  # first call runs eagerly (set-up)
     hom.synchronize()
@@ -604,7 +606,8 @@ def run_gpu_arm(args, cfg, workload):
                 "l2": "no explicit flush: the per-step working set (all layer weights + "
                       "activations) exceeds the 126 MB L2",
                 "launch": "CUDA-graph replay of the runner-utils call sequence"
-                          + (" with the fused embedding extension" if args.fused_embedding else ""),
+                          + (" with the fused embedding extension" if args.fused_embedding else "")
+                          + (" with the fused GEMM+LayerNorm extension" if args.fused_layernorm else ""),
             },
             "model_tflops": value * flops_per_seq / 1e12,
             "e2e": {"value": e2e_value, "unit": "sequences/s", "h2d_bytes_per_step": h2d,
@@ -632,6 +635,10 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bert-base")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused-layernorm", action="store_true",
+                    help="replace the GEMM + LayerNorm call pairs (out-projection, FFN2) by "
+                         "homGemmResidualLayernormF16 (an extension; off by default like "
+                         "--fused-embedding)")
     ap.add_argument("--fused-embedding", action="store_true",
                     help="replace the five embedding calls by homBertEmbeddingF16 (same bits; not "
                          "the call sequence the reference's lowering emits, so off by default)")

@@ -137,6 +137,7 @@ _SIGNATURES = {
     "homSetConstantDir": (None, [c_char_p]),
     "homResidualLayernormF16": (None, _MEMREF * 5 + [c_float]),
     "homBertEmbeddingF16": (None, _MEMREF * 6 + [c_float]),
+    "homGemmResidualLayernormF16": (None, _MEMREF * 2 + [ctypes.c_bool] + _MEMREF * 2 + [c_float]),
     "homLayernormGemmF16NoAlloc": (None, _MEMREF * 6 + [c_float, c_float]),
     "homKernelLaunchCount": (c_int64, []),
     "homOpTimingEnable": (None, [ctypes.c_int]),
@@ -245,6 +246,11 @@ class RunnerUtils:
     def homResidualLayernormF16(self, X, R, gamma, beta, Out, eps=1e-12):
         self.lib.homResidualLayernormF16(*_as_args(X), *_as_args(R), *_as_args(gamma),
                                          *_as_args(beta), *_as_args(Out), eps)
+        self.check()
+
+    def homGemmResidualLayernormF16(self, A, B, R, D, eps=1e-12, weights_nk=False):
+        self.lib.homGemmResidualLayernormF16(*_as_args(A), *_as_args(B), bool(weights_nk), *_as_args(R),
+                                             *_as_args(D), eps)
         self.check()
 
     def homBertEmbeddingF16(self, ids, types, word, pos, type_emb, Out, eps=1e-12):

@@ -15,7 +15,8 @@ from . import REPLAY_LIB, HomError, MemRef, UnrankedMemRef, runner
 class _Config(ctypes.Structure):
     _fields_ = [("layers", c_int32), ("hidden", c_int32), ("heads", c_int32), ("ffn", c_int32),
                 ("vocab", c_int32), ("type_vocab", c_int32), ("batch", c_int32), ("seq", c_int32),
-                ("eps", c_float), ("weights_nk", c_int32), ("fused_embedding", c_int32)]
+                ("eps", c_float), ("weights_nk", c_int32), ("fused_embedding", c_int32),
+                ("fused_layernorm", c_int32)]
 
 
 @dataclass(frozen=True)
@@ -111,13 +112,13 @@ class BertProgram:
     """One replay program: a model configuration at a fixed [batch, seq] on the current GPU."""
 
     def __init__(self, cfg: BertConfig, batch: int, seq: int, weights_nk: bool = False,
-                 fused_embedding: bool = False):
+                 fused_embedding: bool = False, fused_layernorm: bool = False):
         self.cfg, self.batch, self.seq, self.weights_nk = cfg, batch, seq, weights_nk
-        self.fused_embedding = fused_embedding
+        self.fused_embedding, self.fused_layernorm = fused_embedding, fused_layernorm
         self._lib = _replay_lib()
         self._hom = runner()
         c = _Config(cfg.layers, cfg.hidden, cfg.heads, cfg.ffn, cfg.vocab, cfg.type_vocab, batch,
-                    seq, cfg.eps, int(weights_nk), int(fused_embedding))
+                    seq, cfg.eps, int(weights_nk), int(fused_embedding), int(fused_layernorm))
         self._handle = self._lib.homBertCreate(ctypes.byref(c))
         if not self._handle:
             self._hom.check()

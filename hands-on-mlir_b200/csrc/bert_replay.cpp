@@ -148,11 +148,19 @@ int issue_forward(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void
     gemm(p.x, wqkv, p.qkv, p.qkv, 0, 0.0f);
     nvteBertAttentionF16(p.qkv.rank, p.qkv.desc, p.cu.rank, p.cu.desc, p.ctx.rank, p.ctx.desc, scale,
                          c.heads);
-    gemm(p.ctx, wo, p.x, p.x, 0, 1.0f);  // residual: C aliases D
-    nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
-    gemm(p.x, w1, p.ffn, p.ffn, 1, 0.0f);  // erf GELU
-    gemm(p.ffn, w2, p.x, p.x, 0, 1.0f);
-    nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+    if (c.fused_layernorm) {
+      homGemmResidualLayernormF16(p.ctx.rank, p.ctx.desc, wo.rank, wo.desc, c.weights_nk != 0, p.x.rank,
+                                  p.x.desc, p.x.rank, p.x.desc, c.eps);
+      gemm(p.x, w1, p.ffn, p.ffn, 1, 0.0f);  // erf GELU
+      homGemmResidualLayernormF16(p.ffn.rank, p.ffn.desc, w2.rank, w2.desc, c.weights_nk != 0, p.x.rank,
+                                  p.x.desc, p.x.rank, p.x.desc, c.eps);
+    } else {
+      gemm(p.ctx, wo, p.x, p.x, 0, 1.0f);  // residual: C aliases D
+      nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+      gemm(p.x, w1, p.ffn, p.ffn, 1, 0.0f);  // erf GELU
+      gemm(p.ffn, w2, p.x, p.x, 0, 1.0f);
+      nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+    }
   }
   return status();
 }
@@ -464,7 +472,7 @@ void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d2h_bytes) {
 
 int32_t homBertLaunchesPerForward(void *program) {
   auto *p = static_cast<Program *>(program);
-  return p ? (p->cfg.fused_embedding ? 2 : 6) + 7 * p->cfg.layers : 0;
+  return p ? (p->cfg.fused_embedding ? 2 : 6) + (p->cfg.fused_layernorm ? 5 : 7) * p->cfg.layers : 0;
 }
 
 }  // extern "C"

@@ -207,5 +207,112 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
   }
 }
 
+// Epilogue of the fused GEMM + residual + LayerNorm kernel.  The CTAs of one cluster hold the
+// N / BN column tiles of the same 128 rows, so together they hold whole output rows.
+//   pass 1: x = fp16(acc + R) - the value the unfused GEMM would have written - goes into the
+//           warp's staging tile, and the thread's sum and sum of squares of its row over the
+//           warp's 64 columns go to `stats` (shared memory, [4 column groups][128 rows] float2);
+//   cluster barrier; every thread adds up the partials of its row from all column groups of
+//           all CTAs of the cluster (distributed shared memory) -> mean and 1/sqrt(var + eps);
+//   pass 2: the staged values are normalised in place and the tile is handed to TMA.
+// Every thread of the CTA must reach the two cluster barriers: a warp whose column group lies
+// outside the tile (`active` false) publishes zeros and only takes part in the barriers; the
+// second barrier (keeps `stats` alive while peers read it) is the caller's.
+struct LayernormFusion {
+  uint32_t stats_smem;  // shared-memory address of this CTA's float2 stats[4][128]
+  int cluster_n;        // CTAs per cluster = column tiles per row
+  int row_in_tile;      // 32 * lane quarter + lane
+  int group;            // this warp's column group
+  float eps, inv_n;
+};
+
+__device__ __forceinline__ void epilogue_warp_block_ln(const EpilogueParams &ep, const CUtensorMap *tmD,
+                                                       uint32_t tmem_addr, int row0, int c0, bool active,
+                                                       uint32_t stage_smem, int lane, uint4 (&cval)[8],
+                                                       const LayernormFusion &ln) {
+  using namespace hom::ptx;
+  const uint32_t my_row = stage_smem + lane * 128;
+  float s1 = 0.f, s2 = 0.f;
+  if (active) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t acc[32];
+      tmem_ld_32x32(tmem_addr + half * 32, acc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[half * 4 + g]);
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i0 = g * 8 + 2 * j;
+          float2 v = make_float2(__uint_as_float(acc[i0]), __uint_as_float(acc[i0 + 1]));
+          if (ep.c_mode != 0) {
+            const float2 r = __half22float2(h2[j]);
+            v.x += r.x;
+            v.y += r.y;
+          }
+          const __half2 h = __floats2half2_rn(v.x, v.y);
+          const float2 q = __half22float2(h);  // statistics of the rounded values, like the LN kernel sees
+          const bool in0 = c0 + half * 32 + i0 < ep.N, in1 = c0 + half * 32 + i0 + 1 < ep.N;
+          s1 += (in0 ? q.x : 0.f) + (in1 ? q.y : 0.f);
+          s2 = fmaf(in0 ? q.x : 0.f, q.x, s2);
+          s2 = fmaf(in1 ? q.y : 0.f, q.y, s2);
+          w[j] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        const uint32_t addr = my_row + ((static_cast<uint32_t>(half * 4 + g) ^ (lane & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                     "r"(w[2]), "r"(w[3])
+                     : "memory");
+      }
+    }
+  }
+  const uint32_t my_stat = ln.stats_smem + static_cast<uint32_t>(ln.group * 128 + ln.row_in_tile) * 8u;
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(my_stat), "f"(s1), "f"(s2) : "memory");
+  cluster_sync_all();  // partial statistics of every CTA of the cluster are published
+
+  float t1 = 0.f, t2 = 0.f;
+  for (int cta = 0; cta < ln.cluster_n; ++cta) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t remote = map_to_cta(ln.stats_smem + static_cast<uint32_t>(g * 128 + ln.row_in_tile) * 8u,
+                                         static_cast<uint32_t>(cta));
+      float a, b;
+      asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(remote) : "memory");
+      t1 += a;
+      t2 += b;
+    }
+  }
+  const float mean = t1 * ln.inv_n;
+  const float var = fmaxf(fmaf(t2, ln.inv_n, -mean * mean), 0.f);
+  const float rstd = rsqrtf(var + ln.eps);
+  if (!active) return;
+
+#pragma unroll
+  for (int chunk = 0; chunk < 8; ++chunk) {
+    const uint32_t addr = my_row + ((static_cast<uint32_t>(chunk) ^ (lane & 7u)) << 4);
+    uint32_t w[4];
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "r"(addr)
+                 : "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 q = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+      const __half2 h = __floats2half2_rn((q.x - mean) * rstd, (q.y - mean) * rstd);
+      w[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3])
+                 : "memory");
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, stage_smem, c0, row0);
+    bulk_commit_group();
+  }
+}
+
 }  // namespace gemm
 }  // namespace hom

@@ -60,6 +60,9 @@ struct Params {
   int *status;
   long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
   long long *tl;    // optional launch-timeline slot (diagnostics), else null
+  // fused LayerNorm over the output rows (LN kernels only): grid = tiles, one cluster per 128 rows
+  float ln_eps, ln_inv_n;
+  int ln_cluster;
 };
 
 // Wait that ignores the CTA abort flag; used only to let in-flight TMA land before exit.
@@ -70,7 +73,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   }
 }
 
-template <int BN, bool B_NK>
+template <int BN, bool B_NK, bool LN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const Params p) {
@@ -196,6 +199,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (n_st > 0) mbar_wait_drain(full_bar(st), (n_st - 1u) & 1u);
         }
       }
+      if constexpr (LN) cluster_sync_all();  // the epilogue's statistics exchange counts every thread
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
@@ -259,6 +263,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         p.prof[3] = t_full;
         p.prof[4] = t_acc;
       }
+      if constexpr (LN) cluster_sync_all();  // the epilogue's statistics exchange counts every thread
     }
   } else {
     // --------------------------------------------------------------- epilogue
@@ -268,6 +273,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const bool active = col_begin < BN;
     const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
     int it = 0;
+    bool ln_done = false;
     long long t_wait = 0, t_begin = clock64();
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
@@ -285,10 +291,27 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_after_sync();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + col_begin;
-      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem, lane,
-                          cval, [&]() {
-                            if (lane == 0) mbar_arrive(tempty_bar(acc));
-                          });
+      if constexpr (LN) {
+        // one tile per CTA; the pipeline stages are idle by now and stage 0 holds the statistics
+        LayernormFusion ln;
+        ln.stats_smem = smem_base;
+        ln.cluster_n = p.ln_cluster;
+        ln.row_in_tile = quarter * 32 + lane;
+        ln.group = group;
+        ln.eps = p.ln_eps;
+        ln.inv_n = p.ln_inv_n;
+        epilogue_warp_block_ln(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem,
+                               lane, cval, ln);
+        ln_done = true;
+      } else {
+        epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem, lane,
+                            cval, [&]() {
+                              if (lane == 0) mbar_arrive(tempty_bar(acc));
+                            });
+      }
+    }
+    if constexpr (LN) {
+      if (!ln_done) cluster_sync_all();  // error path: keep the cluster barrier's count whole
     }
     // A store still in flight reads this warp's staging tile: let it finish reading.
     if (lane == 0) bulk_wait_group_read_0();
@@ -300,6 +323,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 
   tc_fence_before_sync();
+  if constexpr (LN) cluster_sync_all();  // peers may still be reading this CTA's statistics
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
@@ -566,6 +590,68 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
     return false;
   if (p.prof) profile_report("gemm 1-CTA", p.num_tiles, grid, p.num_kb, stream);
   return check_cuda(cudaGetLastError(), "gemm kernel launch");
+}
+
+// D = LayerNorm(fp16(A.B + R)) over the last dimension: one cluster of pb.N / BN CTAs per 128
+// rows (grid = tiles); R in pb.C (c_mode 1) or absent.
+template <int BN, bool B_NK>
+bool launch_ln_variant(const Problem &pb, float eps, cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kernel = gemm_f16_kernel<BN, B_NK, true>;
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm + layernorm)"))
+      return false;
+    attr_set[dev] = true;
+  }
+  CUtensorMap tmA, tmB, tmD;
+  if (!make_tensor_map_2d(pb.A, pb.K, pb.M, BK, BM, &tmA)) return false;
+  if (!make_tensor_map_2d(pb.D, pb.N, pb.M, 64, 32, &tmD)) return false;
+  if (B_NK) {
+    if (!make_tensor_map_2d(pb.B, pb.K, pb.N, BK, BN, &tmB)) return false;
+  } else {
+    if (!make_tensor_map_grouped(pb.B, pb.N, pb.K, BK, BN / 64, &tmB)) return false;
+  }
+  Params p;
+  p.b_grouped = B_NK ? 0 : 1;
+  p.ep.M = static_cast<int>(pb.M);
+  p.ep.N = static_cast<int>(pb.N);
+  p.K = static_cast<int>(pb.K);
+  p.ep.C = pb.C;
+  p.ep.ldc = pb.N;
+  p.ep.c_mode = pb.c_mode;
+  p.ep.D = pb.D;
+  p.ep.ldd = pb.N;
+  p.ep.alpha = 1.f;
+  p.ep.beta = 1.f;
+  p.ep.act = 0;
+  p.ep.row_scale = nullptr;
+  p.ep.row_shift = nullptr;
+  p.ep.col_sum = nullptr;
+  p.ep.unaligned_n = 0;
+  const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
+  p.n_blocks = static_cast<int>(pb.N / BN);
+  p.num_tiles = m_blocks * p.n_blocks;
+  p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
+  p.stages = Cfg::kStages;
+  p.status = device_status_word();
+  p.prof = nullptr;
+  p.tl = nullptr;
+  p.ln_eps = eps;
+  p.ln_inv_n = 1.f / static_cast<float>(pb.N);
+  p.ln_cluster = p.n_blocks;
+  const double flops = 2.0 * pb.M * pb.N * pb.K;
+  const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
+                              static_cast<double>(pb.M) * pb.N) +
+                       (pb.c_mode == 1 ? 2.0 * pb.M * pb.N : 0.0);
+  LaunchScope scope(kOpGemm, flops, bytes);
+  return check_cuda(launch_pdl(kernel, dim3(p.num_tiles), dim3(kThreads), Cfg::kSmemBytes, stream,
+                               static_cast<unsigned>(p.n_blocks), tmA, tmB, tmD, p),
+                    "gemm + layernorm kernel launch");
 }
 
 struct ShapeRow {
@@ -871,6 +957,44 @@ int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, i
   if (stages) *stages = kTileRows[row].stages;
   if (split_k) *split_k = 1;
   return row;
+}
+
+bool layernorm_fusion_shape(int64_t n, int *cluster_n, int *bn) {
+  for (int c : {1, 2, 4, 8}) {
+    if (n % c != 0) continue;
+    const int64_t w = n / c;
+    if (w == 64 || w == 128 || w == 192 || w == 256) {
+      if (cluster_n) *cluster_n = c;
+      if (bn) *bn = static_cast<int>(w);
+      return true;
+    }
+  }
+  return false;
+}
+
+bool run_layernorm_fused(const Problem &pb, float eps, cudaStream_t stream) {
+  if (pb.M == 0 || pb.N == 0) return true;
+  int cluster_n = 0, bn = 0;
+  if (!layernorm_fusion_shape(pb.N, &cluster_n, &bn)) {
+    set_error(HOM_ERR_UNSUPPORTED,
+              "fused GEMM + LayerNorm needs N = c x {64,128,192,256} with c in {1,2,4,8} (got N = %lld)",
+              static_cast<long long>(pb.N));
+    return false;
+  }
+  if (pb.b_is_nk) {
+    switch (bn) {
+      case 64: return launch_ln_variant<64, true>(pb, eps, stream);
+      case 128: return launch_ln_variant<128, true>(pb, eps, stream);
+      case 192: return launch_ln_variant<192, true>(pb, eps, stream);
+      default: return launch_ln_variant<256, true>(pb, eps, stream);
+    }
+  }
+  switch (bn) {
+    case 64: return launch_ln_variant<64, false>(pb, eps, stream);
+    case 128: return launch_ln_variant<128, false>(pb, eps, stream);
+    case 192: return launch_ln_variant<192, false>(pb, eps, stream);
+    default: return launch_ln_variant<256, false>(pb, eps, stream);
+  }
 }
 
 bool run(const Problem &pb, int tile_row, cudaStream_t stream) {

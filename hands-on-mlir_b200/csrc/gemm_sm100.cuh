@@ -29,6 +29,12 @@ struct Problem {
 // CTA pair per 256 x {128,256} tile; anything else lets the tile table / heuristic decide.
 // Returns false (error recorded) on failure.
 bool run(const Problem &pb, int tile_row, cudaStream_t stream);
+// D = LayerNorm(fp16(A.B + C)) over the last dimension, no affine (C: c_mode 0 or 1; alpha, beta,
+// act of `pb` are ignored): the GEMM kernel with one cluster of N-tile CTAs per 128 rows that
+// exchange row statistics through distributed shared memory.  N must factor as c x
+// {64,128,192,256} with c in {1,2,4,8} (layernorm_fusion_shape).
+bool run_layernorm_fused(const Problem &pb, float eps, cudaStream_t stream);
+bool layernorm_fusion_shape(int64_t n, int *cluster_n, int *bn);
 // The CTA-pair kernels (gemm_pair_sm100.cu); bn2 is 128 or 256.
 bool run_pair(const Problem &pb, int bn2, cudaStream_t stream);
 

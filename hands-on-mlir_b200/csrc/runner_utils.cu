@@ -666,6 +666,28 @@ void homResidualLayernormF16(int64_t rankX, void *dstX, int64_t rankR, void *dst
                          hom::current_stream());
 }
 
+void homGemmResidualLayernormF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB, bool weightsNK,
+                                 int64_t rankR, void *dstR, int64_t rankD, void *dstD, float eps) {
+  const char *name = "homGemmResidualLayernormF16";
+  hom::gemm::Problem pb;
+  bool empty = false;
+  const bool has_r = dstR != nullptr && rankR > 0;
+  if (!gemm_prepare(name, weightsNK, rankA, dstA, rankB, dstB, rankR, dstR, rankD, dstD, 0, 1.f,
+                    has_r ? 1.f : 0.f, &pb, &empty))
+    return;
+  if (pb.c_mode == 2) {
+    set_error(HOM_ERR_UNSUPPORTED, "%s: the residual must have the shape of the output", name);
+    return;
+  }
+  if (!hom::gemm::layernorm_fusion_shape(pb.N, nullptr, nullptr)) {
+    set_error(HOM_ERR_UNSUPPORTED,
+              "%s: N = %lld does not factor as c x {64,128,192,256} with c in {1,2,4,8}", name,
+              static_cast<long long>(pb.N));
+    return;
+  }
+  hom::gemm::run_layernorm_fused(pb, eps, hom::current_stream());
+}
+
 void homBertEmbeddingF16(int64_t rankIds, void *dstIds, int64_t rankTypes, void *dstTypes,
                          int64_t rankWord, void *dstWord, int64_t rankPos, void *dstPos,
                          int64_t rankTypeEmb, void *dstTypeEmb, int64_t rankOut, void *dstOut,

@@ -190,6 +190,19 @@ HOM_EXPORT void homSetConstantDir(const char *dir);
  * unchanged.  A weight directory that cannot be written just runs uncached. */
 HOM_EXPORT void homSetConstantCache(int enable);
 
+/* D = LayerNorm(fp16(A.B + R)) over the last dimension, no affine: what a GEMM with the
+ * residual as C (beta 1) followed by nvteLayernormF16 leaves in D, in one launch.  The CTAs that
+ * hold the column tiles of the same 128 rows form a thread-block cluster and exchange their row
+ * sums through distributed shared memory, so the normalised rows are the only thing written.
+ * A [.., M, K] fp16; B [1, K, N] (weightsNK false) or [1, N, K] (true); R [.., M, N] or a rank-0
+ * descriptor (absent), may alias D; N must be c x {64,128,192,256} with c in {1,2,4,8} (256, 512,
+ * 768, 1024, 1536, 2048, ...).  Statistics in fp32 from the fp16-rounded values (sum and sum of
+ * squares).  No counterpart in the reference: it fuses the call pairs out-projection + LayerNorm
+ * and FFN2 + LayerNorm of the lowered encoder layer. */
+HOM_EXPORT void homGemmResidualLayernormF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
+                                            bool weightsNK, int64_t rankR, void *dstR, int64_t rankD,
+                                            void *dstD, float eps);
+
 /* The embedding stage of the lowered BERT in one launch: what the five calls
  * thrustGatherF16(ids, word) ; thrustGatherF16(types, typeEmb) ; thrustElementwiseAddF16 x2 ;
  * nvteLayernormF16 leave in Out, bit for bit (each fp16 addition rounded, fp32 statistics, no

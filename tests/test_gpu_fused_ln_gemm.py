@@ -75,3 +75,77 @@ def test_rejects_bad_statistics_operands(hom, cuda, pkg):
         hom.cutlassGemmWithVarMeanF16(A, B, D, D, short, ok)
     with pytest.raises(pkg.HomError):
         hom.cutlassLayernormGemmF16(A, B, D, D, ok, short)
+
+
+# ----------------------------------------------------- GEMM + residual + LayerNorm in one launch
+
+@pytest.mark.parametrize("m,n,k,nk,res", [(4096, 768, 768, False, True), (512, 768, 3072, False, True),
+                                          (300, 1024, 264, False, True), (129, 256, 64, False, False),
+                                          (100, 512, 136, True, True), (257, 1536, 72, False, True),
+                                          (64, 2048, 128, True, False), (1, 64, 8, False, True),
+                                          (130, 192, 200, False, True)])
+def test_gemm_residual_layernorm_fused(hom, cuda, oracle, m, n, k, nk, res):
+    """homGemmResidualLayernormF16 against the oracle's GEMM(+residual) -> fp16 -> LayerNorm, and
+    against the two library calls it stands for."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(100 + m + n))
+    A = rng.uniform(-1, 1, (1, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.05, (1, n, k) if nk else (1, k, n)).astype(np.float16)
+    R = rng.standard_normal((1, m, n)).astype(np.float16) if res else None
+    tA, tB = to_dev(A, cuda), to_dev(B, cuda)
+    # unfused pair on the GPU
+    tX = to_dev(R, cuda) if res else torch.zeros((1, m, n), dtype=torch.float16, device=cuda)
+    (hom.nvteGemmF16 if nk else hom.cutlassGemmF16)(tA, tB, tX, tX, beta=1.0 if res else 0.0)
+    hom.nvteLayernormF16(tX, 1e-5)
+    # fused, residual aliasing the output
+    tD = to_dev(R, cuda) if res else torch.full((1, m, n), float("nan"), dtype=torch.float16, device=cuda)
+    before = hom.launch_count()
+    hom.homGemmResidualLayernormF16(tA, tB, tD if res else None, tD, eps=1e-5, weights_nk=nk)
+    assert hom.launch_count() - before == 1
+    hom.synchronize()
+    want = oracle.layernorm_f16(oracle.gemm_f16(A, B, R, b_is_nk=nk, beta=1.0 if res else 0.0), eps=1e-5)
+    got = tD.cpu().numpy()
+    # two roundings are composed (GEMM output to fp16, then LayerNorm): an accumulator that rounds
+    # the other way than the oracle's double sum moves the normalised value by an ulp or two, so
+    # the criterion is the one for composed ops (>= 99.9 % within 1e-3, everything within 1e-2)
+    from util import assert_end_to_end_close
+    assert_end_to_end_close(got, want, f"fused gemm+ln {m}x{n}x{k}")
+    assert_end_to_end_close(got, tX.cpu().numpy(), f"fused vs unfused pair {m}x{n}x{k}")
+
+
+def test_gemm_residual_layernorm_rejects_unsupported_widths(hom, cuda, pkg):
+    import torch
+    A = torch.zeros((1, 16, 64), dtype=torch.float16, device=cuda)
+    for n in (72, 320, 4096):
+        B = torch.zeros((1, 64, n), dtype=torch.float16, device=cuda)
+        D = torch.zeros((1, 16, n), dtype=torch.float16, device=cuda)
+        before = hom.launch_count()
+        with pytest.raises(pkg.HomError) as e:
+            hom.homGemmResidualLayernormF16(A, B, None, D)
+        assert e.value.code == 2 and hom.launch_count() == before
+
+
+def test_forward_with_fused_layernorm_matches_the_call_sequence(hom, cuda, oracle):
+    from hands_on_mlir_b200.bert_program import BertConfig, BertProgram
+    cfg = BertConfig(layers=2, hidden=768, heads=12, ffn=3072, vocab=2000)
+    B, S = 4, 128
+    rng = np.random.Generator(np.random.PCG64(31))
+    w = {name: rng.normal(0, 0.02, cfg.weight_shape(name, S)).astype(np.float16) for name in cfg.weight_names()}
+    lens = np.array([128, 90, 64, 128])
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.int64)
+    types = np.zeros((B, S), dtype=np.int64)
+    outs = []
+    for fused in (False, True):
+        prog = BertProgram(cfg, B, S, fused_layernorm=fused)
+        prog.set_weights({k: to_dev(v, cuda) for k, v in w.items()})
+        assert prog.launches_per_forward() == 6 + (5 if fused else 7) * cfg.layers
+        res = prog.forward(to_dev(ids, cuda), to_dev(mask, cuda), to_dev(types, cuda), use_graph=False)
+        outs.append(prog.result_to_torch(res).cpu().numpy())
+        hom.synchronize()
+        prog.close()
+    want = oracle.bert_encoder(w, ids, mask, types, heads=cfg.heads, eps=cfg.eps)
+    from util import assert_end_to_end_close
+    for b, nvalid in enumerate(lens):
+        assert_end_to_end_close(outs[1][b, :nvalid], want[b, :nvalid], f"fused-LN forward, sequence {b}")
+        assert_end_to_end_close(outs[1][b, :nvalid], outs[0][b, :nvalid], f"fused vs unfused forward, sequence {b}")
