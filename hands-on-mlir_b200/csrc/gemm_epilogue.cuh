@@ -219,7 +219,7 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
 // outside the tile (`active` false) publishes zeros and only takes part in the barriers; the
 // second barrier (keeps `stats` alive while peers read it) is the caller's.
 struct LayernormFusion {
-  uint32_t stats_smem;  // shared-memory address of this CTA's float2 stats[4][128]
+  uint32_t stats_smem;  // shared-memory address of this CTA's float2 stats[4][128] + totals[128]
   int cluster_n;        // CTAs per cluster = column tiles per row
   int row_in_tile;      // 32 * lane quarter + lane
   int group;            // this warp's column group
@@ -269,19 +269,44 @@ __device__ __forceinline__ void epilogue_warp_block_ln(const EpilogueParams &ep,
   }
   const uint32_t my_stat = ln.stats_smem + static_cast<uint32_t>(ln.group * 128 + ln.row_in_tile) * 8u;
   asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(my_stat), "f"(s1), "f"(s2) : "memory");
-  cluster_sync_all();  // partial statistics of every CTA of the cluster are published
-
-  float t1 = 0.f, t2 = 0.f;
-  for (int cta = 0; cta < ln.cluster_n; ++cta) {
+  // The sixteen epilogue warps of this CTA meet (named barrier 1), then the warps of column
+  // group 0 add up the four partials of their rows: one float2 per row and CTA crosses the
+  // cluster instead of four.
+  asm volatile("bar.sync 1, 512;" ::: "memory");
+  if (ln.group == 0) {
+    float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const uint32_t remote = map_to_cta(ln.stats_smem + static_cast<uint32_t>(g * 128 + ln.row_in_tile) * 8u,
-                                         static_cast<uint32_t>(cta));
       float a, b;
-      asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(remote) : "memory");
-      t1 += a;
-      t2 += b;
+      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
+                   : "=f"(a), "=f"(b)
+                   : "r"(ln.stats_smem + static_cast<uint32_t>(g * 128 + ln.row_in_tile) * 8u)
+                   : "memory");
+      c1 += a;
+      c2 += b;
     }
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(ln.stats_smem + 4096u + static_cast<uint32_t>(ln.row_in_tile) * 8u),
+                 "f"(c1), "f"(c2)
+                 : "memory");
+  }
+  cluster_sync_all();  // the row totals of every CTA of the cluster are published
+
+  float ra[8], rb[8];
+#pragma unroll
+  for (int cta = 0; cta < 8; ++cta) {
+    ra[cta] = 0.f;
+    rb[cta] = 0.f;
+    if (cta < ln.cluster_n) {
+      const uint32_t remote = map_to_cta(ln.stats_smem + 4096u + static_cast<uint32_t>(ln.row_in_tile) * 8u,
+                                         static_cast<uint32_t>(cta));
+      asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(ra[cta]), "=f"(rb[cta]) : "r"(remote) : "memory");
+    }
+  }
+  float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+  for (int cta = 0; cta < 8; ++cta) {
+    t1 += ra[cta];
+    t2 += rb[cta];
   }
   const float mean = t1 * ln.inv_n;
   const float var = fmaxf(fmaf(t2, ln.inv_n, -mean * mean), 0.f);

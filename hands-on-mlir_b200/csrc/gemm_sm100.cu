@@ -311,7 +311,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if constexpr (LN) {
-      if (!ln_done) cluster_sync_all();  // error path: keep the cluster barrier's count whole
+      if (!ln_done) {  // error path: keep the named barrier's and the cluster barrier's counts whole
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        cluster_sync_all();
+      }
     }
     // A store still in flight reads this warp's staging tile: let it finish reading.
     if (lane == 0) bulk_wait_group_read_0();
