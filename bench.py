@@ -313,10 +313,11 @@ def run_op_arm(args):
             B = randn(1, k, n, std=0.02)
             D = randn(1, m, n) if prm["c"] == "residual" else torch.empty((1, m, n), dtype=torch.float16, device=dev)
             C = (torch.rand((1, 1, n), generator=g, device=dev) * 2 - 1).half() if prm["c"] == "bias" else D
+            hom.declare_weights(B)  # weights, as in the model: never written by a kernel
             sets.append((A, B, C, D))
         beta = 1.0 if prm["c"] else 0.0
         launch = lambda s: hom.cutlassGemmF16(s[0], s[1], s[2], s[3], activation=prm["act"], beta=beta,
-                                              gemmNum=args.tile)
+                                              gemmNum=args.tile, splitKFactor=args.split)
         flops = 2.0 * m * n * k
         nbytes = per_set + (2 * m * n if prm["c"] == "residual" else 2 * n if prm["c"] else 0)
         bound, work, unit, peak = "tensor", flops, "TFLOP/s", peaks["bf16_tflops"]
@@ -646,6 +647,8 @@ def main():
                     help="time one kernel of the path on its own instead of the whole encoder")
     ap.add_argument("--tile", type=int, default=0,
                     help="with --op gemm-*: force tile-table row 1..4 (0 = automatic)")
+    ap.add_argument("--split", type=int, default=1,
+                    help="with --op gemm-*: K parts per output tile (1 = the library's choice)")
     ap.add_argument("--shape", default=None, help="with --op gemm-*: override M,N,K")
     ap.add_argument("--l2-resident", action="store_true",
                     help="with --op: reuse one buffer set (L2-resident figure)")

@@ -12,9 +12,13 @@ import ctypes
 from ctypes import c_bool, c_char_p, c_double, c_float, c_int32, c_int64, c_void_p
 from pathlib import Path
 
+import os
+
 PKG_DIR = Path(__file__).resolve().parent
-RUNNER_LIB = PKG_DIR / "lib" / "libhands_on_mlir_nvgpu_runner_utils.so"
-REPLAY_LIB = PKG_DIR / "lib" / "libhom_bert_replay.so"
+# HOM_LIB_DIR selects another build of the same two libraries (e.g. lib/diagnostics).
+_LIB_DIR = Path(os.environ["HOM_LIB_DIR"]).resolve() if os.environ.get("HOM_LIB_DIR") else PKG_DIR / "lib"
+RUNNER_LIB = _LIB_DIR / "libhands_on_mlir_nvgpu_runner_utils.so"
+REPLAY_LIB = _LIB_DIR / "libhom_bert_replay.so"
 
 
 class HomError(RuntimeError):
@@ -135,6 +139,8 @@ _SIGNATURES = {
     "homGetStream": (c_void_p, []),
     "homSynchronize": (ctypes.c_int, []),
     "homSetConstantDir": (None, [c_char_p]),
+    "homDeclareWeights": (None, [c_void_p, c_int64]),
+    "homForgetWeights": (None, [c_void_p]),
     "homResidualLayernormF16": (None, _MEMREF * 5 + [c_float]),
     "homBertEmbeddingF16": (None, _MEMREF * 6 + [c_float]),
     "homGemmResidualLayernormF16": (None, _MEMREF * 2 + [ctypes.c_bool] + _MEMREF * 2 + [c_float]),
@@ -201,6 +207,14 @@ class RunnerUtils:
     def use_torch_stream(self):
         import torch
         self.set_stream(torch.cuda.current_stream().cuda_stream)
+
+    def declare_weights(self, tensor):
+        """Tell the library that no kernel writes `tensor` (a GEMM weight): its tiles may then be
+        prefetched before the previous kernel of the stream has finished."""
+        self.lib.homDeclareWeights(c_void_p(tensor.data_ptr()), tensor.numel() * tensor.element_size())
+
+    def forget_weights(self, tensor):
+        self.lib.homForgetWeights(c_void_p(tensor.data_ptr()))
 
     # ------------------------------------------------------------------ compute
     def _gemm(self, fn, A, B, C, D, transa, transb, act, alpha, beta, gemm_num, split_k):

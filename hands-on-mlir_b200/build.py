@@ -9,6 +9,11 @@
   lib/libhom_bert_replay.so                    the BERT call-sequence replay program
 
 nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.
+
+`python hands-on-mlir_b200/build.py --diagnostics` builds a second copy of both libraries
+under lib/diagnostics/ with -DHOM_DIAGNOSTICS (role cycle counters, launch timelines and the
+experiment knobs read from the environment); set HOM_LIB_DIR to that directory to load it.
+The product build contains none of that code.
 """
 from __future__ import annotations
 
@@ -62,8 +67,8 @@ def _newest_header_mtime() -> float:
     return max(f.stat().st_mtime for f in files)
 
 
-def _compile(src: Path, obj: Path, verbose: bool) -> None:
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+def _compile(src: Path, obj: Path, verbose: bool, extra: tuple[str, ...] = ()) -> None:
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
     if src.suffix == ".cpp":
         cmd[1:1] = ["-x", "cu"]
     if verbose:
@@ -82,10 +87,14 @@ def _link(objs: list[Path], out: Path, extra: list[str], verbose: bool) -> None:
         raise RuntimeError(f"link failed for {out.name}:\n{proc.stdout}\n{proc.stderr}")
 
 
-def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
+def build(force: bool = False, verbose: bool = False, diagnostics: bool = False) -> dict[str, Path]:
     """Compile what is out of date and return the paths of the two libraries."""
-    LIB_DIR.mkdir(exist_ok=True)
-    OBJ_DIR.mkdir(exist_ok=True)
+    lib_dir = LIB_DIR / "diagnostics" if diagnostics else LIB_DIR
+    obj_dir = OBJ_DIR / "diagnostics" if diagnostics else OBJ_DIR
+    runner_lib, replay_lib = lib_dir / RUNNER_LIB.name, lib_dir / REPLAY_LIB.name
+    extra = ("-DHOM_DIAGNOSTICS",) if diagnostics else ()
+    lib_dir.mkdir(parents=True, exist_ok=True)
+    obj_dir.mkdir(parents=True, exist_ok=True)
     hdr_mtime = _newest_header_mtime()
     jobs = []
     objs: dict[str, Path] = {}
@@ -93,28 +102,28 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
         src = CSRC / name
         if not src.exists():
             continue
-        obj = OBJ_DIR / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         objs[name] = obj
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_mtime)
         if stale:
             jobs.append((src, obj))
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
-        for fut in [pool.submit(_compile, s, o, verbose) for s, o in jobs]:
+        for fut in [pool.submit(_compile, s, o, verbose, extra) for s, o in jobs]:
             fut.result()
 
     runner_objs = [objs[n] for n in RUNNER_SOURCES if n in objs]
-    if force or jobs or not RUNNER_LIB.exists():
-        _link(runner_objs, RUNNER_LIB, [], verbose)
+    if force or jobs or not runner_lib.exists():
+        _link(runner_objs, runner_lib, [], verbose)
     replay_objs = [objs[n] for n in REPLAY_SOURCES if n in objs]
-    if replay_objs and (force or jobs or not REPLAY_LIB.exists()):
-        _link(replay_objs, REPLAY_LIB,
-              [f"-L{LIB_DIR}", "-lhands_on_mlir_nvgpu_runner_utils", "-ldl", "-Xlinker",
+    if replay_objs and (force or jobs or not replay_lib.exists()):
+        _link(replay_objs, replay_lib,
+              [f"-L{lib_dir}", "-lhands_on_mlir_nvgpu_runner_utils", "-ldl", "-Xlinker",
                "-rpath=$ORIGIN"],
               verbose)
-    return {"runner": RUNNER_LIB, "replay": REPLAY_LIB}
+    return {"runner": runner_lib, "replay": replay_lib}
 
 
 if __name__ == "__main__":
-    out = build(force="--force" in sys.argv, verbose=True)
+    out = build(force="--force" in sys.argv, verbose=True, diagnostics="--diagnostics" in sys.argv)
     for k, v in out.items():
         print(f"{k}: {v} ({'ok' if v.exists() else 'missing'})")

@@ -18,6 +18,7 @@
 
 #include "attention_sm100.cuh"
 #include "gemm_sm100.cuh"
+#include "hom_diag.cuh"
 #include "ptx_sm100.cuh"
 
 namespace hom {
@@ -45,8 +46,8 @@ struct Params {
   int seq, heads;
   float scale_log2;  // softmax scale * log2(e)
   int *status;
-  long long *prof;  // phase stamps of two CTAs (diagnostic, HOM_ATTN_PROFILE), else null
-  int timeline_slot;  // >= 0: record first/last CTA entry and exit times instead (HOM_ATTN_TIMELINE)
+  HOM_DIAG(long long *prof;)     // phase stamps of two CTAs (HOM_ATTN_PROFILE), else null
+  HOM_DIAG(int timeline_slot;)   // >= 0: record first/last CTA entry and exit times instead
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -71,7 +72,6 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
-  pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int row = tid & (kTile - 1);
@@ -120,6 +120,9 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmQKV, const Params p) 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Dependents may be scheduled only now that this CTA holds its tensor memory (a CTA that
+  // returned above counts as having triggered).
+  pdl_launch_dependents();
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + 128;
   const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -353,14 +356,14 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - raw_addr);
 
-  pdl_launch_dependents();
-  const long long t_entry = clock64();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int row = tid & (kTile - 1);
   const int hf = tid >> 7;  // which half of the key columns / output columns
   const int head = blockIdx.y, batch = blockIdx.z;
   const int hidden = p.heads * kHeadDim;
+#if HOM_DIAG_ENABLED
+  const long long t_entry = clock64();
   long long *stamps = nullptr;
   if (p.prof != nullptr && tid == 0 && p.timeline_slot >= 0) {
     const long long now = static_cast<long long>(global_ns());
@@ -383,6 +386,9 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
     if (cta_ns && slot == 6) cta_ns[2] = static_cast<long long>(global_ns());
     if (cta_ns && slot == 9) cta_ns[3] = static_cast<long long>(global_ns());
   };
+#else
+  auto stamp = [](int) {};
+#endif
 
   const uint32_t smem_q = smem_base, smem_k = smem_base + kTileBytes, smem_v = smem_base + 2 * kTileBytes;
   const uint32_t smem_p = smem_base;  // two 128 x 64 sub-tiles over Q|K
@@ -410,6 +416,8 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_acc = *tmem_slot;
+  // Dependents may be scheduled only now that every CTA of this grid holds its tensor memory.
+  pdl_launch_dependents();
   const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
   stamp(0);
 
@@ -610,22 +618,41 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
     tc_fence_after_sync();
     tmem_dealloc(tmem_acc, 128);
   }
-  if (p.prof != nullptr && tid == 0 && p.timeline_slot >= 0) {
+  HOM_DIAG(if (p.prof != nullptr && tid == 0 && p.timeline_slot >= 0) {
     const long long now = static_cast<long long>(global_ns());
     atomicMin(p.prof + 34 + 4 * p.timeline_slot, now);
     atomicMax(p.prof + 35 + 4 * p.timeline_slot, now);
-  }
+  })
 }
 
 }  // namespace
 
 namespace {
 
+// Identity of a cached output tensor map: the whole (pointer, shape) tuple is compared, the
+// hash only picks the bucket.
+struct OutMapKey {
+  const void *ptr;
+  uint64_t hidden, seq, bs;
+  bool operator==(const OutMapKey &o) const {
+    return ptr == o.ptr && hidden == o.hidden && seq == o.seq && bs == o.bs;
+  }
+};
+struct OutMapKeyHash {
+  size_t operator()(const OutMapKey &k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ k.hidden;
+    h = h * 1000003u ^ k.seq;
+    h = h * 1000003u ^ k.bs;
+    return h;
+  }
+};
+
 // Output [bs, seq, hidden] fp16 as a 3-D tensor (hidden, seq, bs) with 64 x 128 x 1 boxes.
 bool make_out_map(const void *ptr, uint64_t hidden, uint64_t seq, uint64_t bs, CUtensorMap *out) {
   static std::mutex mu;
-  static std::unordered_map<uint64_t, CUtensorMap> cache;
-  const uint64_t key = reinterpret_cast<uint64_t>(ptr) ^ (hidden << 48) ^ (seq << 32) ^ (bs << 20);
+  static std::unordered_map<OutMapKey, CUtensorMap, OutMapKeyHash> cache;
+  const OutMapKey key{ptr, hidden, seq, bs};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -690,6 +717,7 @@ bool run(const Problem &pb, cudaStream_t stream) {
   p.heads = static_cast<int>(pb.heads);
   p.scale_log2 = pb.scale * 1.44269504088896340736f;
   p.status = device_status_word();
+#if HOM_DIAG_ENABLED
   static const bool want_prof = std::getenv("HOM_ATTN_PROFILE") != nullptr;
   p.prof = nullptr;
   p.timeline_slot = -1;
@@ -702,6 +730,7 @@ bool run(const Problem &pb, cudaStream_t stream) {
       p.prof = gemm::profile_buffer();
     }
   }
+#endif
   dim3 grid(static_cast<unsigned>((pb.seq + kTile - 1) / kTile), static_cast<unsigned>(pb.heads),
             static_cast<unsigned>(pb.bs));
   const double d = kHeadDim;
@@ -722,6 +751,7 @@ bool run(const Problem &pb, cudaStream_t stream) {
     const bool launched = check_cuda(launch_pdl(attention_f16_single_tile_kernel, grid, dim3(kThreads1),
                                                 kSmemBytes1, stream, 1, tm, tm_out, p),
                                      "attention kernel launch");
+#if HOM_DIAG_ENABLED
     if (p.prof && p.timeline_slot < 0) {
       long long h[32];
       cudaStreamSynchronize(stream);
@@ -733,6 +763,7 @@ bool run(const Problem &pb, cudaStream_t stream) {
                 c ? "mid" : "0", h[16 * c], h[16 * c + 1], h[16 * c + 2], h[16 * c + 3], h[16 * c + 4],
                 h[16 * c + 5], h[16 * c + 6], h[16 * c + 7], h[16 * c + 8], h[16 * c + 9]);
     }
+#endif
     return launched;
   }
   return check_cuda(launch_pdl(attention_f16_kernel, grid, dim3(kThreads), kSmemBytes, stream, 1, tm, p),

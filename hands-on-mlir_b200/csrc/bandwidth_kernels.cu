@@ -8,6 +8,7 @@
 #include <cstdlib>
 
 #include "bandwidth_kernels.cuh"
+#include "hom_diag.cuh"
 #include "ptx_sm100.cuh"
 
 namespace hom {
@@ -457,10 +458,10 @@ bool layernorm_f16(const __half *x, const __half *res, const __half *gamma, cons
   // One launch wave of few, large blocks starts sooner (measured 4.4 vs 4.8 us at 4096 x 768);
   // with many waves, small blocks retire and refill more evenly (5.27 vs 4.64 TB/s at 131072 rows).
   int warps_per_block = rows <= 8192 ? 16 : 4;
-  if (const char *env = std::getenv("HOM_LN_WARPS")) {  // experiment knob
+  HOM_DIAG(if (const char *env = std::getenv("HOM_LN_WARPS")) {  // experiment knob
     const int v = std::atoi(env);
     if (v == 4 || v == 8 || v == 16) warps_per_block = v;
-  }
+  })
   const unsigned blocks = static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block);
   const unsigned threads = 32u * warps_per_block;
   const bool vec_ok = hidden % 8 == 0 && hidden <= 32 * 8 * 16 && aligned16(x) && aligned16(out) &&

@@ -301,6 +301,13 @@ int homBertSetWeight(void *program, int32_t index, int64_t rank, void *descripto
   t.desc = copy;
   t.owned_desc = true;
   p->weights[index] = t;
+  {
+    // The program never writes its weights: let the GEMMs prefetch them early.
+    const int64_t *w = static_cast<const int64_t *>(copy);
+    int64_t n = 1;
+    for (int64_t i = 0; i < rank; ++i) n *= w[3 + i];
+    homDeclareWeights(reinterpret_cast<const char *>(static_cast<void *const *>(copy)[1]) + 2 * w[2], 2 * n);
+  }
   if (p->graph_exec) {
     cudaGraphExecDestroy(p->graph_exec);
     p->graph_exec = nullptr;

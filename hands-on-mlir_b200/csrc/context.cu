@@ -3,8 +3,10 @@
 // CUDA error (include/NVGPUKernels/Utils.h:45-52) and always uses the null stream.
 #include <atomic>
 #include <cstdlib>
+#include <map>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "hom_common.cuh"
@@ -39,6 +41,12 @@ struct TimingRecord {
 std::mutex g_timing_mutex;
 std::vector<TimingRecord> g_timing_log;
 std::atomic<bool> g_timing_enabled{false};
+
+// Device address ranges that hold constants (weights): begin -> end.  A GEMM whose B operand
+// lies inside one may request its first B tiles before the previous kernel of the stream has
+// finished, because no kernel writes a constant.
+std::mutex g_const_mutex;
+std::map<uintptr_t, uintptr_t> g_const_ranges;
 
 DeviceState &device_state() {
   int dev = 0;
@@ -78,6 +86,84 @@ bool check_cuda(cudaError_t e, const char *what) {
 
 cudaStream_t current_stream() { return tl_stream; }
 
+namespace {
+struct SplitBuffers {
+  float *slots = nullptr;
+  size_t slot_floats = 0;
+  int *counters = nullptr;
+  size_t counter_ints = 0;
+  uint64_t clean_epoch = 0;
+};
+thread_local std::map<std::pair<int, cudaStream_t>, SplitBuffers> tl_split;
+std::atomic<uint64_t> g_split_dirty_epoch{0};
+}  // namespace
+
+void split_workspace_mark_dirty() { g_split_dirty_epoch.fetch_add(1); }
+
+bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, SplitWorkspace *out) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  SplitBuffers &b = tl_split[{dev, stream}];
+  if (b.slot_floats < slot_floats) {
+    // Round up generously: the typical caller alternates between a few shapes.
+    size_t want = slot_floats < (size_t{8} << 20) ? (size_t{8} << 20) : slot_floats + slot_floats / 2;
+    if (b.slots) cudaFree(b.slots);  // waits for the kernels that may still use it
+    b.slots = nullptr;
+    b.slot_floats = 0;
+    void *ptr = nullptr;
+    if (!check_cuda(cudaMalloc(&ptr, want * sizeof(float)), "cudaMalloc(split-K partials)")) return false;
+    b.slots = static_cast<float *>(ptr);
+    b.slot_floats = want;
+  }
+  const uint64_t epoch = g_split_dirty_epoch.load();
+  const size_t ints = blocks;
+  if (b.counter_ints < ints) {
+    size_t want = ints < (size_t{1} << 16) ? (size_t{1} << 16) : 2 * ints;
+    if (b.counters) cudaFree(b.counters);
+    b.counters = nullptr;
+    b.counter_ints = 0;
+    void *ptr = nullptr;
+    if (!check_cuda(cudaMalloc(&ptr, want * sizeof(int)), "cudaMalloc(split-K counters)")) return false;
+    if (!check_cuda(cudaMemset(ptr, 0, want * sizeof(int)), "cudaMemset(split-K counters)")) {
+      cudaFree(ptr);
+      return false;
+    }
+    b.counters = static_cast<int *>(ptr);
+    b.counter_ints = want;
+    b.clean_epoch = epoch;
+  } else if (b.clean_epoch != epoch) {
+    // A kernel gave up a wait since these counters were last known clean.
+    if (!check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize(split-K counters)")) return false;
+    if (!check_cuda(cudaMemset(b.counters, 0, b.counter_ints * sizeof(int)), "cudaMemset(split-K counters)"))
+      return false;
+    b.clean_epoch = epoch;
+  }
+  out->slots = b.slots;
+  out->counters = b.counters;
+  return true;
+}
+
+void declare_constant_range(const void *ptr, size_t bytes) {
+  if (!ptr || bytes == 0) return;
+  const uintptr_t b = reinterpret_cast<uintptr_t>(ptr);
+  std::lock_guard<std::mutex> lock(g_const_mutex);
+  g_const_ranges[b] = b + bytes;
+}
+
+void forget_constant_range(const void *ptr) {
+  std::lock_guard<std::mutex> lock(g_const_mutex);
+  g_const_ranges.erase(reinterpret_cast<uintptr_t>(ptr));
+}
+
+bool is_constant_range(const void *ptr, size_t bytes) {
+  const uintptr_t b = reinterpret_cast<uintptr_t>(ptr);
+  std::lock_guard<std::mutex> lock(g_const_mutex);
+  auto it = g_const_ranges.upper_bound(b);
+  if (it == g_const_ranges.begin()) return false;
+  --it;
+  return b >= it->first && b + bytes <= it->second;
+}
+
 bool pdl_enabled() {
   static const bool on = std::getenv("HOM_DISABLE_PDL") == nullptr;
   return on;
@@ -109,9 +195,9 @@ void record_event(cudaEvent_t ev, cudaStream_t stream) {
 }
 }  // namespace
 
-LaunchScope::LaunchScope(OpKind kind, double flops, double bytes) {
+LaunchScope::LaunchScope(OpKind kind, double flops, double bytes, bool may_allocate) {
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
-  if (!g_timing_enabled.load(std::memory_order_relaxed)) return;
+  if (!may_allocate || !g_timing_enabled.load(std::memory_order_relaxed)) return;
   TimingRecord rec{kind, flops, bytes, nullptr, nullptr};
   if (cudaEventCreate(&rec.start) != cudaSuccess) return;
   if (cudaEventCreate(&rec.stop) != cudaSuccess) {
@@ -146,6 +232,12 @@ void homClearLastError(void) {
   if (st.status_host) st.status_host[0] = 0;
 }
 
+void homDeclareWeights(const void *ptr, int64_t bytes) {
+  if (bytes > 0) hom::declare_constant_range(ptr, static_cast<size_t>(bytes));
+}
+
+void homForgetWeights(const void *ptr) { hom::forget_constant_range(ptr); }
+
 void homSetStream(void *stream) { hom::tl_stream = static_cast<cudaStream_t>(stream); }
 
 void *homGetStream(void) { return hom::tl_stream; }
@@ -158,6 +250,7 @@ int homSynchronize(void) {
   }
   auto &st = hom::device_state();
   if (st.status_host && st.status_host[0] != 0) {
+    hom::split_workspace_mark_dirty();
     hom::set_error(HOM_ERR_DEVICE_TIMEOUT, "a device-side wait expired (kernel status %d)",
                    st.status_host[0]);
   }

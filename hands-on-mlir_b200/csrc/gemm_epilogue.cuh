@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 #include <cstdint>
 
+#include "hom_diag.cuh"
 #include "ptx_sm100.cuh"
 
 namespace hom {
@@ -31,6 +32,9 @@ struct EpilogueParams {
   // element by element and D is written by the warp from its staging tile with 4- or 2-byte
   // stores instead of a TMA store.
   int unaligned_n;
+  // Diagnostics builds: bit mask that removes parts of the epilogue (1 accumulator read,
+  // 2 arithmetic, 4 staging stores, 8 global store, 16 C read, 32 everything but the release).
+  HOM_DIAG(int dbg;)
 };
 
 // GELU on two values at once for the tile epilogues, built so that the special-function unit
@@ -58,6 +62,29 @@ __device__ __forceinline__ float2 gelu_erf_fast2(float2 x) {
   return __ffma2_rn(make_float2(-a.x, -a.y), t, relu);
 }
 
+// ---------------------------------------------------------------------------- split-K
+// A tile whose K range is cut into `parts` work units is reduced serially, in part order, by
+// the epilogue warps that own the same [32 rows x 64 columns] block of the tile in each unit
+// (the scheme of a serial split-K semaphore).  The block has one fp32 slot in the workspace and
+// one counter that holds the number of parts already folded into the slot:
+//   part 0            writes its accumulator block to the slot and sets the counter to 1;
+//   part q (0<q<last) waits for counter == q, adds its block to the slot, sets counter = q + 1;
+//   the last part     waits for counter == parts - 1, adds the slot to its accumulator (taken
+//                     straight from tensor memory), applies the epilogue, resets the counter.
+// The sum is therefore always ((p0 + p1) + p2) + ...: bit-identical from run to run.  A part
+// only ever waits for parts with a lower unit number; units are handed out in increasing order
+// to CTAs that are all resident, so those parts are running or finished: every wait ends (and
+// is bounded anyway).  Slot layout is private to the block: chunk j of lane l at float offset
+// j * 128 + l * 4, so every load and store instruction moves 512 contiguous bytes.
+// The counters are zero whenever no GEMM is in flight (zeroed at allocation, reset after use).
+struct SplitK {
+  int parts = 1;   // K parts per tile (1: no split)
+  int part = 0;    // this unit's part index
+  float *slot = nullptr;   // this block's kSplitSlotFloats floats of workspace
+  int *counter = nullptr;  // this block's counter
+};
+constexpr int kSplitSlotFloats = 32 * 64;
+
 // Epilogue warps per CTA and the shared-memory staging each of them owns.  Sixteen warps -
 // four per tensor-memory lane quarter, each draining one 64-column group of the tile - put
 // four epilogue warps on every scheduler: the epilogue arithmetic (dependent FMA / SFU chains)
@@ -65,21 +92,28 @@ __device__ __forceinline__ float2 gelu_erf_fast2(float2 x) {
 // 64-column block per warp instead of two.  Each warp stages its [32 rows x 64 fp16 columns]
 // block in one 128-byte-swizzled tile that a TMA store then writes out.
 constexpr int kEpilogueWarps = 16;
+// Warp 0 is the TMA producer, warp 1 issues the MMAs, the epilogue warps follow.
+constexpr int kControlWarps = 2;
 constexpr uint32_t kEpilogueTileBytes = 32 * 128;
 constexpr uint32_t kEpilogueStageBytes = kEpilogueTileBytes;
 constexpr uint32_t kEpilogueStagingBytes = kEpilogueWarps * kEpilogueStageBytes;
 
 // Requests the residual / bias values of one 64-column row segment (row `row`, columns
-// [c0, c0 + 64)); out-of-range groups come back as zeros.
+// [c0, c0 + 64)), or of its 8-column groups [G0, G1) only; out-of-range groups come back as zeros.
+template <int G0 = 0, int G1 = 8>
 __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int row, int c0, uint4 (&cval)[8]) {
   if (ep.c_mode == 0) return;
+  HOM_DIAG(if (ep.dbg & 48) {
+    for (int g = G0; g < G1; ++g) cval[g] = make_uint4(0, 0, 0, 0);
+    return;
+  })
   const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
   const bool row_ok = ep.c_mode == 2 || row < ep.M;
   if (ep.unaligned_n) {
     // element-wise reads, packed in registers (no addressable array: keeps cval out of local memory)
     const unsigned short *cu = reinterpret_cast<const unsigned short *>(cp);
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
+    for (int g = G0; g < G1; ++g) {
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -93,7 +127,7 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
     return;
   }
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
+  for (int g = G0; g < G1; ++g) {
     const bool ok = row_ok && c0 + g * 8 < ep.N;
     cval[g] = ok ? *reinterpret_cast<const uint4 *>(cp + g * 8) : make_uint4(0, 0, 0, 0);
   }
@@ -110,17 +144,93 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
 // After the last accumulator read the function calls `release()` (the accumulator may be
 // overwritten) while the store drains.  A warp whose column group lies outside the tile
 // (`active` false) only releases.
-template <typename Release>
-__device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
+// Returns false only when a split-K wait expired (the CTA's abort flag is then set).
+template <bool SPLIT = false, typename Release>
+__device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
                                                     uint32_t tmem_addr, int row0, int c0, bool active,
                                                     uint32_t stage_smem, int lane, uint4 (&cval)[8],
-                                                    Release release) {
+                                                    Release release, const SplitK sk = SplitK(),
+                                                    volatile int *abort_flag = nullptr, int *status = nullptr) {
   using namespace hom::ptx;
-  if (!active) {
+  if (!active HOM_DIAG(|| (ep.dbg & 32))) {
     tc_fence_before_sync();
     __syncwarp();
     release();
-    return;
+    return true;
+  }
+  if constexpr (SPLIT) {
+    const bool last = sk.part == sk.parts - 1;
+    if (sk.part > 0) {
+      // Wait until the parts before this one are in the slot.  One lane polls (with an acquire
+      // load); the warp barrier that follows orders the other lanes' slot reads after it.
+      bool ok = true;
+      if (lane == 0 HOM_DIAG(&& !(ep.dbg & 64))) {
+        const long long t0 = clock64();
+        for (uint32_t it = 0;; ++it) {
+          int have;
+          asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(have) : "l"(sk.counter) : "memory");
+          if (have >= sk.part) break;
+          if ((it & 15u) == 15u && ((abort_flag && *abort_flag) || clock64() - t0 > kWaitLimitCycles)) {
+            ok = false;
+            break;
+          }
+          __nanosleep(100);
+        }
+      }
+      __syncwarp();
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          if (abort_flag) *abort_flag = 1;
+          if (status) {
+            atomicCAS(status, 0, static_cast<int>(kDevWaitTimeoutEpilogue));
+            __threadfence_system();
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        release();
+        return false;
+      }
+    }
+    if (!last) {
+      float *slot = sk.slot + lane * 4;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t acc[32];
+        tmem_ld_32x32(tmem_addr + half * 32, acc);
+        tmem_ld_wait();
+        if (half == 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          release();
+        }
+        if (sk.part > 0) {
+          float4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4 *>(slot + (half * 8 + j) * 128));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[4 * j] = __float_as_uint(v[j].x + __uint_as_float(acc[4 * j]));
+            acc[4 * j + 1] = __float_as_uint(v[j].y + __uint_as_float(acc[4 * j + 1]));
+            acc[4 * j + 2] = __float_as_uint(v[j].z + __uint_as_float(acc[4 * j + 2]));
+            acc[4 * j + 3] = __float_as_uint(v[j].w + __uint_as_float(acc[4 * j + 3]));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          __stcg(reinterpret_cast<uint4 *>(slot + (half * 8 + j) * 128),
+                 make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+      }
+      HOM_DIAG(if (!(ep.dbg & 128)))
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(sk.counter), "r"(sk.part + 1) : "memory");
+      return true;
+    }
+    // Last part: every lane has seen the counter; nobody else will touch it before the next launch.
+    __syncwarp();
+    if (lane == 0) *sk.counter = 0;
   }
   const int row = row0 + lane;
   const uint32_t my_row = stage_smem + lane * 128;
@@ -134,8 +244,34 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     uint32_t acc[32];
-    tmem_ld_32x32(tmem_addr + half * 32, acc);
-    tmem_ld_wait();
+#if HOM_DIAG_ENABLED
+    if (ep.dbg & 1) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = 0x3f000000u + lane;
+    } else
+#endif
+    {
+      tmem_ld_32x32(tmem_addr + half * 32, acc);
+      tmem_ld_wait();
+    }
+    if constexpr (SPLIT) {
+      // acc <- (p0 + ... + p_{last-1}) + p_last, the left operand being what the slot holds.
+      // The residual / bias values of this half are requested together with the slot (the
+      // caller fetches nothing ahead of time for a split tile: registers).
+      const float *slot = sk.slot + lane * 4 + half * 8 * 128;
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4 *>(slot + j * 128));
+      if (half == 0) epilogue_load_c<0, 4>(ep, row, c0, cval);
+      else epilogue_load_c<4, 8>(ep, row, c0, cval);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[4 * j] = __float_as_uint(v[j].x + __uint_as_float(acc[4 * j]));
+        acc[4 * j + 1] = __float_as_uint(v[j].y + __uint_as_float(acc[4 * j + 1]));
+        acc[4 * j + 2] = __float_as_uint(v[j].z + __uint_as_float(acc[4 * j + 2]));
+        acc[4 * j + 3] = __float_as_uint(v[j].w + __uint_as_float(acc[4 * j + 3]));
+      }
+    }
     if (half == 1) {
       tc_fence_before_sync();
       __syncwarp();
@@ -161,13 +297,21 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
       for (int j = 0; j < 4; ++j) {
         const int i0 = g * 8 + 2 * j;
         float2 v = make_float2(__uint_as_float(acc[i0]), __uint_as_float(acc[i0 + 1]));
-        if (!unit_alpha) v = __fmul2_rn(alpha2, v);  // alpha * x is exact for alpha == 1: skip it
-        if (ep.c_mode != 0) v = __ffma2_rn(beta2, __half22float2(h2[j]), v);
-        if (ep.act == 1) v = gelu_erf_fast2(v);
+        HOM_DIAG(if (!(ep.dbg & 2))) {
+          if (!unit_alpha) v = __fmul2_rn(alpha2, v);  // alpha * x is exact for alpha == 1: skip it
+          if (ep.c_mode != 0) v = __ffma2_rn(beta2, __half22float2(h2[j]), v);
+          if (ep.act == 1) v = gelu_erf_fast2(v);
+        }
         const __half2 h = __floats2half2_rn(v.x, v.y);
         w[j] = *reinterpret_cast<const uint32_t *>(&h);
       }
       const uint32_t addr = my_row + ((static_cast<uint32_t>(half * 4 + g) ^ (lane & 7u)) << 4);
+#if HOM_DIAG_ENABLED
+      if (ep.dbg & 4) {
+        asm volatile("" ::"r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]));
+        continue;
+      }
+#endif
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
                    "r"(w[2]), "r"(w[3])
                    : "memory");
@@ -177,7 +321,7 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      if (c0 < ep.N && row0 < ep.M) tma_store_2d(tmD, stage_smem, c0, row0);
+      if (c0 < ep.N && row0 < ep.M HOM_DIAG(&& !(ep.dbg & 8))) tma_store_2d(tmD, stage_smem, c0, row0);
       bulk_commit_group();
     }
   } else {
@@ -205,6 +349,7 @@ __device__ __forceinline__ void epilogue_warp_block(const EpilogueParams &ep, co
     }
     __syncwarp();
   }
+  return true;
 }
 
 // Epilogue of the fused GEMM + residual + LayerNorm kernel.  The CTAs of one cluster hold the

@@ -16,6 +16,7 @@
 // Hand-offs: full[s] lives in the even CTA (armed by its producer for the bytes of both CTAs);
 // empty[s] and acc_full[a] exist in both CTAs and are signalled by tcgen05.commit addressed to
 // both; acc_empty[a] lives in the even CTA (16 arrivals: 8 epilogue warps x 2 CTAs).
+#include <cstdio>
 #include <cstdlib>
 
 #include "gemm_epilogue.cuh"
@@ -30,7 +31,7 @@ using namespace hom::ptx;
 namespace {
 
 constexpr int BK = 64;
-constexpr int kPairThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kPairThreads = 32 * (kControlWarps + kEpilogueWarps);
 constexpr uint32_t kABytes = 128 * BK * 2;
 
 template <int BN2>
@@ -51,12 +52,19 @@ struct PairParams {
   int n_blocks, num_tiles, num_kb;
   int stages;
   int b_grouped;  // B [K,N] is fetched through the grouped 3-D tensor map (N % 64 == 0)
+  int b_early;    // B is a declared constant: request its first tiles before griddepcontrol.wait
+  // Split-K: every tile is cut into `split_k` work units (K-block ranges); num_units = num_tiles
+  // * split_k.  Workspace: per (tile, CTA of the pair, epilogue warp) `split_k` fp32 slots and a
+  // pair of counters (see SplitK in gemm_epilogue.cuh).
+  int split_k, num_units;
+  float *ws_slots;
+  int *ws_counters;
   int *status;
-  long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
-  long long *tl;    // optional launch-timeline slot (diagnostics), else null
+  HOM_DIAG(long long *prof;)  // optional per-role cycle counters of CTA 0, else null
+  HOM_DIAG(long long *tl;)    // optional launch-timeline slot, else null
 };
 
-template <int BN2, bool B_NK>
+template <int BN2, bool B_NK, bool SPLIT = false>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const PairParams p) {
@@ -86,8 +94,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  pdl_launch_dependents();
-  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);
+  HOM_DIAG(if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -108,6 +115,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Dependents may be scheduled only now that this grid's CTAs hold their tensor memory.
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -122,7 +131,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      long long t_wait = 0, t_begin = clock64();
+      HOM_DIAG(long long t_wait = 0; const long long t_begin = clock64();)
       const uint32_t full_even_base = map_to_cta(full_bar(0), 0);
       auto full_even = [&](int slot) { return full_even_base + 8u * slot; };
       auto arm = [&](int slot) {
@@ -143,30 +152,35 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             tma_load_2d_pair(b_dst + g * (BK * 128), &tmB, full_even(slot), nb0 + g * 64, kb * BK);
         }
       };
-      // B holds weights, which no earlier kernel of the stream writes: the first ring of B
-      // tiles is requested before waiting for the previous kernel, A only after.
+      // When B is a declared constant (weights, which no kernel of the stream writes) the
+      // first ring of B tiles is requested before waiting for the previous kernel; A, and a B
+      // of unknown origin, only after.
       int pre = 0;
-      if (pair < p.num_tiles) {
-        const int nb0 = (pair % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
-        pre = p.num_kb < stages_used ? p.num_kb : stages_used;
-        for (int kb = 0; kb < pre; ++kb) {
-          arm(kb);
-          load_b(kb, kb, nb0);
+      if (p.b_early && pair < p.num_units) {
+        const int tile0 = pair / p.split_k, part0 = pair % p.split_k;
+        const int nb0 = (tile0 % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
+        const int kb0 = part0 * p.num_kb / p.split_k, kb1 = (part0 + 1) * p.num_kb / p.split_k;
+        pre = kb1 - kb0 < stages_used ? kb1 - kb0 : stages_used;
+        for (int i = 0; i < pre; ++i) {
+          arm(i);
+          load_b(i, kb0 + i, nb0);
         }
       }
       pdl_wait();
-      if (p.tl && leader) timeline_stamp(p.tl, 2);
-      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+      HOM_DIAG(if (p.tl && leader) timeline_stamp(p.tl, 2);)
+      for (int unit = pair; unit < p.num_units && ok; unit += num_pairs) {
+        const int tile = unit / p.split_k, part = unit % p.split_k;
         const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
         const int nb0 = (tile % p.n_blocks) * BN2 + static_cast<int>(rank) * HALF;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          const bool b_done = tile == pair && kb < pre;
+        const int kb_begin = part * p.num_kb / p.split_k, kb_end = (part + 1) * p.num_kb / p.split_k;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          const bool b_done = unit == pair && kb - kb_begin < pre;
           if (!b_done) {
-            const long long tw = p.prof ? clock64() : 0;
+            HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
             ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status,
                                                    kDevWaitTimeoutProducer));
             if (!ok) break;
-            if (p.prof) t_wait += clock64() - tw;
+            HOM_DIAG(if (p.prof) t_wait += clock64() - tw;)
             arm(s);
             load_b(s, kb, nb0);
           }
@@ -177,10 +191,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
         }
       }
-      if (p.prof && blockIdx.x < 2 && lane == 0) {
+      HOM_DIAG(if (p.prof && blockIdx.x < 2 && lane == 0) {
         p.prof[0 + 8 * blockIdx.x] = clock64() - t_begin;
         p.prof[1 + 8 * blockIdx.x] = t_wait;
-      }
+      })
       if (!ok) {
         // Give copies already in flight time to land before shared memory is released.
         const long long t0 = clock64();
@@ -199,28 +213,31 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
-      long long t_full = 0, t_acc = 0, t_begin = clock64();
-      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+      HOM_DIAG(long long t_full = 0, t_acc = 0; const long long t_begin = clock64();)
+      for (int unit = pair; unit < p.num_units && ok; unit += num_pairs, ++it) {
+        const int part = unit % p.split_k;
+        const int num_kb = (part + 1) * p.num_kb / p.split_k - part * p.num_kb / p.split_k;
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
-        const long long ta = p.prof ? clock64() : 0;
+        HOM_DIAG(const long long ta = p.prof ? clock64() : 0;)
         ok = __all_sync(0xffffffffu,
                         mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma));
         if (!ok) break;
-        if (p.prof) t_acc += clock64() - ta;
+        HOM_DIAG(if (p.prof) t_acc += clock64() - ta;)
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN2;
         bool have = false;  // full[s] already seen complete by the probe of the previous block
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {
           if (!have) {
-            const long long tw = p.prof ? clock64() : 0;
+            HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
             ok = __all_sync(0xffffffffu,
                             mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma));
             if (!ok) break;
-            if (p.prof) t_full += clock64() - tw;
+            HOM_DIAG(if (p.prof) t_full += clock64() - tw;)
           }
           have = false;
           tc_fence_after_sync();
+          HOM_DIAG(if (p.tl && it == 0 && kb == 0 && leader) timeline_stamp(p.tl, 6);)
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + kABytes;
           const int s_next = s + 1 == stages_used ? 0 : s + 1;
@@ -232,7 +249,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                      : make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024);
             if (leader) tc_mma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             // Probe the next stage while the tensor pipe is busy with what was just queued.
-            if (k == 1 && kb + 1 < p.num_kb)
+            if (k == 1 && kb + 1 < num_kb)
               have = __all_sync(0xffffffffu, mbar_test_wait(full_bar(s_next), ph_next));
           }
           if (leader) tc_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
@@ -241,34 +258,47 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
         if (ok && leader) tc_commit_pair(tfull_bar(acc), 0x3);  // accumulator ready in both CTAs
       }
-      if (p.prof && blockIdx.x == 0 && lane == 0) {
+      HOM_DIAG(if (p.prof && blockIdx.x == 0 && lane == 0) {
         p.prof[2] = clock64() - t_begin;
         p.prof[3] = t_full;
         p.prof[4] = t_acc;
-      }
+      })
     }
-  } else {
+  } else if (warp >= kControlWarps) {
     // --------------------------------------------------------------- epilogue
     const int quarter = warp & 3;       // tensor-memory lanes [32*quarter, +32)
-    const int group = (warp - 2) >> 2;  // which 64-column group of the tile
+    const int group = (warp - kControlWarps) >> 2;  // which 64-column group of the tile
     const int col_begin = group * 64;
     const bool active = col_begin < BN2;
-    const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
+    const uint32_t stage_smem = staging_base + (warp - kControlWarps) * kEpilogueStageBytes;
     int it = 0;
-    long long t_wait = 0, t_begin = clock64();
+    HOM_DIAG(long long t_wait = 0; const long long t_begin = clock64();)
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
-    for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++it) {
+    for (int unit = pair; unit < p.num_units; unit += num_pairs, ++it) {
+      const int tile = unit / p.split_k;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       const int m0 = (tile / p.n_blocks) * 256 + static_cast<int>(rank) * 128;
       const int n0 = (tile % p.n_blocks) * BN2 + col_begin;
       uint4 cval[8];
-      if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cval);
-      const long long tw = p.prof ? clock64() : 0;
+      SplitK sk;
+      if constexpr (SPLIT) {
+        // this warp's block of the tile: (tile, CTA of the pair, epilogue warp)
+        const size_t block = (static_cast<size_t>(tile) * 2 + rank) * kEpilogueWarps + (warp - kControlWarps);
+        sk.parts = p.split_k;
+        sk.part = unit % p.split_k;
+        sk.slot = p.ws_slots + block * kSplitSlotFloats;
+        sk.counter = p.ws_counters + block;
+      } else {
+        if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cval);
+      }
+      HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (p.prof) t_wait += clock64() - tw;
+      HOM_DIAG(if (p.prof) t_wait += clock64() - tw;)
+      HOM_DIAG(if (p.tl && warp == kControlWarps && lane == 0 && unit + num_pairs >= p.num_units)
+                   timeline_stamp(p.tl, 8);)
       tc_fence_after_sync();
       auto release = [&]() {
         if (lane == 0) {
@@ -278,15 +308,17 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       };
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_begin;
-      epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0, active, stage_smem, lane, cval, release);
+      if (!epilogue_warp_block<SPLIT>(p.ep, &tmD, t_row, m0 + quarter * 32, n0, active, stage_smem, lane, cval,
+                               release, sk, abort_flag, p.status))
+        break;
     }
     // A store still in flight reads this warp's staging tile: let it finish reading.
     if (lane == 0) bulk_wait_group_read_0();
     __syncwarp();
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {
+    HOM_DIAG(if (p.prof && blockIdx.x == 0 && threadIdx.x == 32 * kControlWarps) {
       p.prof[5] = clock64() - t_begin;
       p.prof[6] = t_wait;
-    }
+    })
   }
 
   // Nobody leaves while the other CTA may still read this CTA's shared memory (MMA operand
@@ -297,11 +329,11 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
   }
-  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 4);
+  HOM_DIAG(if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 4);)
 }
 
 template <int BN2, bool B_NK>
-bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
+bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   using Cfg = PairCfg<BN2>;
   static bool attr_set[64] = {};
   static int max_clusters[64] = {};
@@ -309,6 +341,7 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   auto kernel = gemm_f16_pair_kernel<BN2, B_NK>;
+  auto kernel_split = gemm_f16_pair_kernel<BN2, B_NK, true>;
 
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
@@ -327,7 +360,10 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   if (!attr_set[dev]) {
     if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
-                    "cudaFuncSetAttribute(gemm pair)"))
+                    "cudaFuncSetAttribute(gemm pair)") ||
+        !check_cuda(cudaFuncSetAttribute(kernel_split, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, split-K)"))
       return false;
     // How many CTA pairs the device can hold at once (pairs need neighbouring SMs).
     cfg.gridDim = dim3(2 * (sm_count() / 2));
@@ -336,12 +372,12 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
       cudaGetLastError();
       n = sm_count() / 2;
     }
-    if (const char *env = std::getenv("HOM_GEMM_PAIRS")) {  // experiment knob
+    HOM_DIAG(if (const char *env = std::getenv("HOM_GEMM_PAIRS")) {  // experiment knob
       const int v = std::atoi(env);
       if (v >= 1) n = v;
     }
     if (std::getenv("HOM_DEBUG"))
-      fprintf(stderr, "[hom] gemm pair BN2=%d nk=%d: %d co-resident CTA pairs\n", BN2, int(B_NK), n);
+      fprintf(stderr, "[hom] gemm pair BN2=%d nk=%d: %d co-resident CTA pairs\n", BN2, int(B_NK), n);)
     max_clusters[dev] = n;
     attr_set[dev] = true;
   }
@@ -363,6 +399,7 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   }
   PairParams p;
   p.b_grouped = grouped ? 1 : 0;
+  p.b_early = pb.b_const ? 1 : 0;
   p.ep.C = pb.C;
   p.ep.ldc = pb.N;
   p.ep.c_mode = pb.c_mode;
@@ -375,6 +412,7 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
+  HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
   p.ep.M = static_cast<int>(pb.M);
   p.ep.N = static_cast<int>(pb.N);
   p.K = static_cast<int>(pb.K);
@@ -383,35 +421,47 @@ bool launch_pair_variant(const Problem &pb, cudaStream_t stream) {
   p.num_tiles = m_blocks * p.n_blocks;
   p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
   p.stages = Cfg::kStages;
-  if (const char *env = std::getenv("HOM_GEMM_STAGES")) {  // experiment knob
+  HOM_DIAG(if (const char *env = std::getenv("HOM_GEMM_STAGES")) {  // experiment knob
     const int v = std::atoi(env);
     if (v >= 1 && v < Cfg::kStages) p.stages = v;
-  }
+  })
   p.status = device_status_word();
-  p.prof = profile_buffer();
-  p.tl = launch_timeline_slot();
-  const int pairs = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
+  HOM_DIAG(p.prof = profile_buffer(); p.tl = launch_timeline_slot();)
+  p.split_k = split_k < 1 ? 1 : split_k > 16 ? 16 : split_k;
+  if (p.split_k > p.num_kb) p.split_k = p.num_kb;
+  p.num_units = p.num_tiles * p.split_k;
+  p.ws_slots = nullptr;
+  p.ws_counters = nullptr;
+  if (p.split_k > 1) {
+    const size_t blocks = static_cast<size_t>(p.num_tiles) * 2 * kEpilogueWarps;
+    SplitWorkspace ws;
+    if (!split_workspace(blocks * kSplitSlotFloats, blocks, stream, &ws)) return false;
+    p.ws_slots = ws.slots;
+    p.ws_counters = ws.counters;
+  }
+  const int pairs = p.num_units < max_clusters[dev] ? p.num_units : max_clusters[dev];
   cfg.gridDim = dim3(2 * pairs);
   const double flops = 2.0 * pb.M * pb.N * pb.K;
   const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
                               static_cast<double>(pb.M) * pb.N) +
                        (pb.c_mode == 1 ? 2.0 * pb.M * pb.N : pb.c_mode == 2 ? 2.0 * pb.N : 0.0);
   LaunchScope scope(kOpGemm, flops, bytes);
-  if (!check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p), "gemm pair kernel launch"))
+  if (!check_cuda(cudaLaunchKernelEx(&cfg, p.split_k > 1 ? kernel_split : kernel, tmA, tmB, tmD, p),
+                  "gemm pair kernel launch"))
     return false;
-  if (p.prof) profile_report("gemm CTA-pair", p.num_tiles, 2 * pairs, p.num_kb, stream);
+  HOM_DIAG(if (p.prof) profile_report("gemm CTA-pair", p.num_tiles, 2 * pairs, p.num_kb, stream);)
   return check_cuda(cudaGetLastError(), "gemm pair kernel launch");
 }
 
 }  // namespace
 
-bool run_pair(const Problem &pb, int bn2, cudaStream_t stream) {
+bool run_pair(const Problem &pb, int bn2, int split_k, cudaStream_t stream) {
   if (pb.b_is_nk) {
-    return bn2 == 128 ? launch_pair_variant<128, true>(pb, stream)
-                      : launch_pair_variant<256, true>(pb, stream);
+    return bn2 == 128 ? launch_pair_variant<128, true>(pb, split_k, stream)
+                      : launch_pair_variant<256, true>(pb, split_k, stream);
   }
-  return bn2 == 128 ? launch_pair_variant<128, false>(pb, stream)
-                    : launch_pair_variant<256, false>(pb, stream);
+  return bn2 == 128 ? launch_pair_variant<128, false>(pb, split_k, stream)
+                    : launch_pair_variant<256, false>(pb, split_k, stream);
 }
 
 }  // namespace gemm

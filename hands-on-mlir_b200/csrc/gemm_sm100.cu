@@ -15,6 +15,7 @@
 // This replaces the reference's CUTLASS 2.x mma.sync kernels and its compile-time autotuner
 // (include/NVGPUKernels/GemmRunner.h:119-310, lib/NVGPUKernels/GemmProfiler.cu:143-236) with a
 // small per-shape tile table.
+#include <algorithm>
 #include <cstdlib>
 #include <cstdio>
 #include <tuple>
@@ -25,6 +26,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "gemm_sm100.cuh"
+#include "hom_diag.cuh"
 #include "ptx_sm100.cuh"
 
 namespace hom {
@@ -36,7 +38,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kThreads = 32 * (kControlWarps + kEpilogueWarps);
 constexpr uint32_t kABytes = BM * BK * 2;
 
 template <int BN>
@@ -57,9 +59,16 @@ struct Params {
   int n_blocks, num_tiles, num_kb;
   int stages;  // ring slots in use, <= TileCfg::kStages
   int b_grouped;  // B [K,N] is fetched through the grouped 3-D tensor map (N % 64 == 0)
+  int b_early;    // B is a declared constant: request its first tiles before griddepcontrol.wait
+  // Split-K: every tile is cut into `split_k` work units (K-block ranges); num_units = num_tiles
+  // * split_k.  Workspace: per (tile, epilogue warp) `split_k` fp32 slots and a pair of counters
+  // (see SplitK in gemm_epilogue.cuh).
+  int split_k, num_units;
+  float *ws_slots;
+  int *ws_counters;
   int *status;
-  long long *prof;  // optional per-role cycle counters of CTA 0 (diagnostics), else null
-  long long *tl;    // optional launch-timeline slot (diagnostics), else null
+  HOM_DIAG(long long *prof;)  // optional per-role cycle counters of CTA 0, else null
+  HOM_DIAG(long long *tl;)    // optional launch-timeline slot, else null
   // fused LayerNorm over the output rows (LN kernels only): grid = tiles, one cluster per 128 rows
   float ln_eps, ln_inv_n;
   int ln_cluster;
@@ -73,7 +82,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   }
 }
 
-template <int BN, bool B_NK, bool LN = false>
+template <int BN, bool B_NK, bool LN = false, bool SPLIT = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const Params p) {
@@ -99,11 +108,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const long long t_entry = p.prof ? clock64() : 0;
-  unsigned long long g_entry = 0;
-  if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
-  pdl_launch_dependents();
-  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);
+  HOM_DIAG(const long long t_entry = p.prof ? clock64() : 0; unsigned long long g_entry = 0;
+           if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
+           if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -124,7 +131,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[10] = clock64() - t_entry;
+  // Dependents may be scheduled from here on: every CTA of this grid that reaches this point
+  // already holds its tensor-memory columns, so a dependent CTA that becomes co-resident and
+  // allocates its own columns can never starve one of ours.
+  pdl_launch_dependents();
+  HOM_DIAG(if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[10] = clock64() - t_entry;)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -139,7 +150,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int s = 0;
       uint32_t ph = 0, armed = 0;
       bool ok = true;
-      long long t_wait = 0, t_begin = clock64();
+      HOM_DIAG(long long t_wait = 0; const long long t_begin = clock64();)
       auto load_b = [&](int slot, int kb, int n0) {
         const uint32_t b_dst = smem_base + slot * Cfg::kStageBytes + kABytes;
         if (!leader) return;
@@ -153,30 +164,35 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tma_load_2d(b_dst + g * (BK * 128), &tmB, full_bar(slot), n0 + g * 64, kb * BK);
         }
       };
-      // B holds weights, which no earlier kernel of the stream writes: the first ring of B
-      // tiles is requested before waiting for the previous kernel, A only after.
+      // When B is a declared constant (weights, which no kernel of the stream writes) the
+      // first ring of B tiles is requested before waiting for the previous kernel; A, and a B
+      // of unknown origin, only after.
       int pre = 0;
-      if (blockIdx.x < p.num_tiles) {
-        const int n0 = (blockIdx.x % p.n_blocks) * BN;
-        pre = p.num_kb < stages_used ? p.num_kb : stages_used;
-        for (int kb = 0; kb < pre; ++kb) {
-          if (leader) mbar_arrive_expect_tx(full_bar(kb), Cfg::kStageBytes);
-          load_b(kb, kb, n0);
+      if (p.b_early && blockIdx.x < p.num_units) {
+        const int tile0 = blockIdx.x / p.split_k, part0 = blockIdx.x % p.split_k;
+        const int n0 = (tile0 % p.n_blocks) * BN;
+        const int kb0 = part0 * p.num_kb / p.split_k, kb1 = (part0 + 1) * p.num_kb / p.split_k;
+        pre = kb1 - kb0 < stages_used ? kb1 - kb0 : stages_used;
+        for (int i = 0; i < pre; ++i) {
+          if (leader) mbar_arrive_expect_tx(full_bar(i), Cfg::kStageBytes);
+          load_b(i, kb0 + i, n0);
         }
       }
       pdl_wait();
-      if (p.tl && leader) timeline_stamp(p.tl, 2);
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      HOM_DIAG(if (p.tl && leader) timeline_stamp(p.tl, 2);)
+      for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x) {
+        const int tile = unit / p.split_k, part = unit % p.split_k;
         const int m0 = (tile / p.n_blocks) * BM;
         const int n0 = (tile % p.n_blocks) * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          const bool b_done = tile == static_cast<int>(blockIdx.x) && kb < pre;
+        const int kb_begin = part * p.num_kb / p.split_k, kb_end = (part + 1) * p.num_kb / p.split_k;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          const bool b_done = unit == static_cast<int>(blockIdx.x) && kb - kb_begin < pre;
           if (!b_done) {
-            const long long tw = p.prof ? clock64() : 0;
+            HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
             ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status,
                                                    kDevWaitTimeoutProducer));
             if (!ok) break;
-            if (p.prof) t_wait += clock64() - tw;
+            HOM_DIAG(if (p.prof) t_wait += clock64() - tw;)
             if (leader) mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
             load_b(s, kb, n0);
           }
@@ -188,10 +204,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
       }
-      if (p.prof && blockIdx.x == 0 && lane == 0) {
+      HOM_DIAG(if (p.prof && blockIdx.x == 0 && lane == 0) {
         p.prof[0] = clock64() - t_begin;
         p.prof[1] = t_wait;
-      }
+      })
       if (!ok) {
         // Let every copy this warp started land before the CTA gives its shared memory back.
         for (int st = 0; st < stages_used; ++st) {
@@ -212,25 +228,27 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
-      long long t_full = 0, t_acc = 0, t_begin = clock64();
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+      HOM_DIAG(long long t_full = 0, t_acc = 0; const long long t_begin = clock64();)
+      for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++it) {
+        const int part = unit % p.split_k;
+        const int num_kb = (part + 1) * p.num_kb / p.split_k - part * p.num_kb / p.split_k;
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
-        const long long ta = p.prof ? clock64() : 0;
+        HOM_DIAG(const long long ta = p.prof ? clock64() : 0;)
         ok = __all_sync(0xffffffffu,
                         mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kDevWaitTimeoutMma));
         if (!ok) break;
-        if (p.prof) t_acc += clock64() - ta;
+        HOM_DIAG(if (p.prof) t_acc += clock64() - ta;)
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool have = false;  // full[s] already seen complete by the probe of the previous block
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {
           if (!have) {
-            const long long tw = p.prof ? clock64() : 0;
+            HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
             ok = __all_sync(0xffffffffu,
                             mbar_wait(full_bar(s), ph, abort_flag, p.status, kDevWaitTimeoutMma));
             if (!ok) break;
-            if (p.prof) t_full += clock64() - tw;
+            HOM_DIAG(if (p.prof) t_full += clock64() - tw;)
           }
           have = false;
           tc_fence_after_sync();
@@ -249,7 +267,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                      : make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024);
             if (leader) tc_mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             // Probe the next stage while the tensor pipe is busy with what was just queued.
-            if (k == 1 && kb + 1 < p.num_kb)
+            if (k == 1 && kb + 1 < num_kb)
               have = __all_sync(0xffffffffu, mbar_test_wait(full_bar(s_next), ph_next));
           }
           if (leader) tc_commit(empty_bar(s));
@@ -258,36 +276,47 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         if (ok && leader) tc_commit(tfull_bar(acc));
       }
-      if (p.prof && blockIdx.x == 0 && lane == 0) {
+      HOM_DIAG(if (p.prof && blockIdx.x == 0 && lane == 0) {
         p.prof[2] = clock64() - t_begin;
         p.prof[3] = t_full;
         p.prof[4] = t_acc;
-      }
+      })
       if constexpr (LN) cluster_sync_all();  // the epilogue's statistics exchange counts every thread
     }
   } else {
     // --------------------------------------------------------------- epilogue
     const int quarter = warp & 3;       // TMEM lanes [32*quarter, 32*quarter + 32)
-    const int group = (warp - 2) >> 2;  // which 64-column group of the tile
+    const int group = (warp - kControlWarps) >> 2;  // which 64-column group of the tile
     const int col_begin = group * 64;
     const bool active = col_begin < BN;
-    const uint32_t stage_smem = staging_base + (warp - 2) * kEpilogueStageBytes;
+    const uint32_t stage_smem = staging_base + (warp - kControlWarps) * kEpilogueStageBytes;
     int it = 0;
     bool ln_done = false;
-    long long t_wait = 0, t_begin = clock64();
+    HOM_DIAG(long long t_wait = 0; const long long t_begin = clock64();)
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < p.num_units; unit += gridDim.x, ++it) {
+      const int tile = unit / p.split_k;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       const int m0 = (tile / p.n_blocks) * BM;
       const int n0 = (tile % p.n_blocks) * BN;
       uint4 cval[8];
-      if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
-      const long long tw = p.prof ? clock64() : 0;
+      SplitK sk;
+      if constexpr (SPLIT) {
+        // this warp's block of the tile: (tile, epilogue warp)
+        const size_t block = static_cast<size_t>(tile) * kEpilogueWarps + (warp - kControlWarps);
+        sk.parts = p.split_k;
+        sk.part = unit % p.split_k;
+        sk.slot = p.ws_slots + block * kSplitSlotFloats;
+        sk.counter = p.ws_counters + block;
+      } else {
+        if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
+      }
+      HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (p.prof) t_wait += clock64() - tw;
+      HOM_DIAG(if (p.prof) t_wait += clock64() - tw;)
       tc_fence_after_sync();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + col_begin;
@@ -304,10 +333,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                lane, cval, ln);
         ln_done = true;
       } else {
-        epilogue_warp_block(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem, lane,
-                            cval, [&]() {
-                              if (lane == 0) mbar_arrive(tempty_bar(acc));
-                            });
+        if (!epilogue_warp_block<SPLIT>(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem,
+                                 lane, cval, [&]() {
+                                   if (lane == 0) mbar_arrive(tempty_bar(acc));
+                                 }, sk, abort_flag, p.status))
+          break;
       }
     }
     if constexpr (LN) {
@@ -319,10 +349,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // A store still in flight reads this warp's staging tile: let it finish reading.
     if (lane == 0) bulk_wait_group_read_0();
     __syncwarp();
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {
+    HOM_DIAG(if (p.prof && blockIdx.x == 0 && threadIdx.x == 32 * kControlWarps) {
       p.prof[5] = clock64() - t_begin;
       p.prof[6] = t_wait;
-    }
+    })
   }
 
   tc_fence_before_sync();
@@ -332,19 +362,19 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
-  if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 4);
-  if (p.prof && blockIdx.x == 0 && threadIdx.x == 32) {
-    unsigned long long g_exit;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_exit));
-    p.prof[11] = clock64() - t_entry;
-    p.prof[12] = static_cast<long long>(g_entry);
-    p.prof[13] = static_cast<long long>(g_exit);
-    // ring of (entry, exit) wall-clock stamps of the last launches (timeline diagnostics)
-    const long long slot = p.prof[15] & 15;
-    p.prof[16 + 2 * slot] = static_cast<long long>(g_entry);
-    p.prof[17 + 2 * slot] = static_cast<long long>(g_exit);
-    p.prof[15] += 1;
-  }
+  HOM_DIAG(if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 4);
+           if (p.prof && blockIdx.x == 0 && threadIdx.x == 32) {
+             unsigned long long g_exit;
+             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_exit));
+             p.prof[11] = clock64() - t_entry;
+             p.prof[12] = static_cast<long long>(g_entry);
+             p.prof[13] = static_cast<long long>(g_exit);
+             // ring of (entry, exit) wall-clock stamps of the last launches
+             const long long slot = p.prof[15] & 15;
+             p.prof[16 + 2 * slot] = static_cast<long long>(g_entry);
+             p.prof[17 + 2 * slot] = static_cast<long long>(g_exit);
+             p.prof[15] += 1;
+           })
 }
 
 // ------------------------------------------------------------------ host side
@@ -391,6 +421,7 @@ std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
 
 }  // namespace
 
+#if HOM_DIAG_ENABLED
 // Diagnostics (HOM_GEMM_PROFILE=1): a small device buffer the kernels fill with per-role
 // cycle counters of CTA 0, printed after a stream synchronisation.  Never on by default.
 static long long *g_profile_buf = nullptr;
@@ -407,10 +438,11 @@ long long *profile_buffer() {
         long long init[32];
         for (int i = 0; i < 32; ++i) init[i] = (i & 1) == 0 ? 0x7fffffffffffffffLL : 0;
         cudaMemcpy(g_profile_buf + 32, init, sizeof(init), cudaMemcpyHostToDevice);
-        // slots [3800, 4088): {first, last} x {entry, dependency resolved, exit} of 48 GEMM launches
-        long long init2[288];
-        for (int i = 0; i < 288; ++i) init2[i] = (i & 1) == 0 ? 0x7fffffffffffffffLL : 0;
-        cudaMemcpy(g_profile_buf + 3800, init2, sizeof(init2), cudaMemcpyHostToDevice);
+        // slots [3000, 3480): {first, last} x {entry, dependency resolved, exit, first MMA issued,
+        // last accumulator complete} of 48 GEMM launches
+        long long init2[480];
+        for (int i = 0; i < 480; ++i) init2[i] = (i & 1) == 0 ? 0x7fffffffffffffffLL : 0;
+        cudaMemcpy(g_profile_buf + 3000, init2, sizeof(init2), cudaMemcpyHostToDevice);
       }
     }
   }
@@ -428,7 +460,7 @@ long long *profile_buffer_raw() { return g_profile_buf; }
 long long *launch_timeline_slot() {
   static int calls = 0;
   if (!g_profile_buf || !std::getenv("HOM_GEMM_LAUNCH_TIMELINE")) return nullptr;
-  return g_profile_buf + 3800 + 6 * (calls++ % 48);
+  return g_profile_buf + 3000 + 10 * (calls++ % 48);
 }
 
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream) {
@@ -443,6 +475,7 @@ void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStrea
           what, tiles, grid, num_kb, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9], h[10], h[11],
           h[12], h[13] - h[12]);
 }
+#endif  // HOM_DIAG_ENABLED
 
 // 2-D fp16 tensor [outer, inner] (inner contiguous), 128-byte swizzle, zero fill.
 bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
@@ -523,17 +556,29 @@ bool make_tensor_map_grouped(const void *ptr, uint64_t cols, uint64_t rows, uint
 
 namespace {
 
+// Splits a tile's K blocks into at most `want` parts of at least one block each.
+int clamp_split(int want, int num_kb) {
+  int s = want < 1 ? 1 : want;
+  if (s > 16) s = 16;
+  if (s > num_kb) s = num_kb;
+  return s;
+}
+
 template <int BN, bool B_NK>
-bool launch_variant(const Problem &pb, cudaStream_t stream) {
+bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   auto kernel = gemm_f16_kernel<BN, B_NK>;
+  auto kernel_split = gemm_f16_kernel<BN, B_NK, false, true>;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
-                    "cudaFuncSetAttribute(gemm)"))
+                    "cudaFuncSetAttribute(gemm)") ||
+        !check_cuda(cudaFuncSetAttribute(kernel_split, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, split-K)"))
       return false;
     attr_set[dev] = true;
   }
@@ -554,6 +599,7 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
   }
   Params p;
   p.b_grouped = grouped ? 1 : 0;
+  p.b_early = pb.b_const ? 1 : 0;
   p.ep.M = static_cast<int>(pb.M);
   p.ep.N = static_cast<int>(pb.N);
   p.K = static_cast<int>(pb.K);
@@ -569,29 +615,40 @@ bool launch_variant(const Problem &pb, cudaStream_t stream) {
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
+  HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
   p.num_tiles = m_blocks * p.n_blocks;
   p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
   p.stages = Cfg::kStages;
-  if (const char *env = std::getenv("HOM_GEMM_STAGES")) {  // experiment knob
+  HOM_DIAG(if (const char *env = std::getenv("HOM_GEMM_STAGES")) {  // experiment knob
     const int v = std::atoi(env);
     if (v >= 1 && v < Cfg::kStages) p.stages = v;
-  }
+  })
   p.status = device_status_word();
-  p.prof = profile_buffer();
-  p.tl = launch_timeline_slot();
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  HOM_DIAG(p.prof = profile_buffer(); p.tl = launch_timeline_slot();)
+  p.split_k = clamp_split(split_k, p.num_kb);
+  p.num_units = p.num_tiles * p.split_k;
+  p.ws_slots = nullptr;
+  p.ws_counters = nullptr;
+  if (p.split_k > 1) {
+    const size_t blocks = static_cast<size_t>(p.num_tiles) * kEpilogueWarps;
+    SplitWorkspace ws;
+    if (!split_workspace(blocks * kSplitSlotFloats, blocks, stream, &ws)) return false;
+    p.ws_slots = ws.slots;
+    p.ws_counters = ws.counters;
+  }
+  const int grid = p.num_units < sm_count() ? p.num_units : sm_count();
   const double flops = 2.0 * pb.M * pb.N * pb.K;
   const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
                               static_cast<double>(pb.M) * pb.N) +
                        (pb.c_mode == 1 ? 2.0 * pb.M * pb.N : pb.c_mode == 2 ? 2.0 * pb.N : 0.0);
   LaunchScope scope(kOpGemm, flops, bytes);
-  if (!check_cuda(launch_pdl(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, 1, tmA, tmB,
-                             tmD, p),
+  if (!check_cuda(launch_pdl(p.split_k > 1 ? kernel_split : kernel, dim3(grid), dim3(kThreads),
+                             Cfg::kSmemBytes, stream, 1, tmA, tmB, tmD, p),
                   "gemm kernel launch"))
     return false;
-  if (p.prof) profile_report("gemm 1-CTA", p.num_tiles, grid, p.num_kb, stream);
+  HOM_DIAG(if (p.prof) profile_report("gemm 1-CTA", p.num_tiles, grid, p.num_kb, stream);)
   return check_cuda(cudaGetLastError(), "gemm kernel launch");
 }
 
@@ -621,6 +678,7 @@ bool launch_ln_variant(const Problem &pb, float eps, cudaStream_t stream) {
   }
   Params p;
   p.b_grouped = B_NK ? 0 : 1;
+  p.b_early = pb.b_const ? 1 : 0;
   p.ep.M = static_cast<int>(pb.M);
   p.ep.N = static_cast<int>(pb.N);
   p.K = static_cast<int>(pb.K);
@@ -636,14 +694,18 @@ bool launch_ln_variant(const Problem &pb, float eps, cudaStream_t stream) {
   p.ep.row_shift = nullptr;
   p.ep.col_sum = nullptr;
   p.ep.unaligned_n = 0;
+  HOM_DIAG(p.ep.dbg = 0;)
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>(pb.N / BN);
   p.num_tiles = m_blocks * p.n_blocks;
   p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
   p.stages = Cfg::kStages;
   p.status = device_status_word();
-  p.prof = nullptr;
-  p.tl = nullptr;
+  HOM_DIAG(p.prof = nullptr; p.tl = nullptr;)
+  p.split_k = 1;
+  p.num_units = p.num_tiles;
+  p.ws_slots = nullptr;
+  p.ws_counters = nullptr;
   p.ln_eps = eps;
   p.ln_inv_n = 1.f / static_cast<float>(pb.N);
   p.ln_cluster = p.n_blocks;
@@ -661,6 +723,7 @@ struct ShapeRow {
   int64_t m, n, k;
   int act;
   int row;
+  int split;
 };
 
 // Tile-table rows: 1-4 = one CTA per 128 x {64,128,192,256} tile; 5, 6 = one CTA pair per
@@ -678,11 +741,11 @@ constexpr int kNumTileRows = 6;
 // Per-shape choices for the BERT-base encoder GEMMs (M = batch*seq rows), replacing the
 // reference's autotune cache keyed on (M, N, K, activation).
 const ShapeRow kShapeTable[] = {
-    {4096, 2304, 768, 0, 6},   // base QKV
-    {4096, 768, 768, 0, 3},    // base attention output projection (+ residual)
-    {4096, 3072, 768, 1, 6},   // base FFN1 + GELU
-    {4096, 768, 3072, 0, 3},   // base FFN2 (+ residual)
-    {512, 3072, 768, 1, 2},    // single fused GEMM + bias + GELU case
+    {4096, 2304, 768, 0, 6, 1},   // base QKV
+    {4096, 768, 768, 0, 3, 1},    // base attention output projection (+ residual)
+    {4096, 3072, 768, 1, 6, 1},   // base FFN1 + GELU
+    {4096, 768, 3072, 0, 3, 1},   // base FFN2 (+ residual)
+    {512, 3072, 768, 1, 2, 1},    // single fused GEMM + bias + GELU case
 };
 
 }  // namespace
@@ -769,31 +832,39 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
+  HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
   p.b_grouped = grouped ? 1 : 0;
+  p.b_early = pb.b_const ? 1 : 0;
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
   p.num_tiles = m_blocks * p.n_blocks;
   p.num_kb = static_cast<int>((pb.K + BK - 1) / BK);
   p.stages = Cfg::kStages;
   p.status = device_status_word_if_ready();
-  p.prof = nullptr;
-  p.tl = nullptr;
+  HOM_DIAG(p.prof = nullptr; p.tl = nullptr;)
+  p.split_k = 1;
+  p.num_units = p.num_tiles;
+  p.ws_slots = nullptr;
+  p.ws_counters = nullptr;
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
   const double flops = 2.0 * pb.M * pb.N * pb.K;
   const double bytes = 2.0 * (static_cast<double>(pb.M) * pb.K + static_cast<double>(pb.K) * pb.N +
                               static_cast<double>(pb.M) * pb.N);
-  LaunchScope scope(kOpGemm, flops, bytes);
+  LaunchScope scope(kOpGemm, flops, bytes, /*may_allocate=*/false);
   return check_cuda(launch_pdl(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, 1, tmA, tmB,
                                tmD, p),
                     "gemm kernel launch");
 }
 
-// ---- tuned shapes: (M, N, K, activation) -> tile-table row, filled by tune() or a cache file.
-// Takes the place of the reference's GemmProfiler timing cache
-// (include/NVGPUKernels/GemmProfiler.h:39-41).
+// ---- tuned shapes: (M, N, K, activation) -> (tile-table row, K split), filled by tune() or a
+// cache file.  Takes the place of the reference's GemmProfiler timing cache
+// (include/NVGPUKernels/GemmProfiler.h:39-41), whose entries are (kernel number, split-K factor).
 namespace {
 using TuneKey = std::tuple<int64_t, int64_t, int64_t, int>;
-std::map<TuneKey, int> g_tuned;
+struct TuneChoice {
+  int row, split;
+};
+std::map<TuneKey, TuneChoice> g_tuned;
 std::mutex g_tuned_mutex;
 
 void load_env_cache_once() {
@@ -813,24 +884,48 @@ __global__ void fill_pattern_kernel(__half *p, size_t n, uint32_t seed, float sc
     p[i] = __float2half((static_cast<float>(h & 0xffff) / 32768.f - 1.f) * scale);
   }
 }
+
+// Candidate K splits for a tile with `num_kb` K blocks: 1..min(16, K / 128) like the
+// reference's sweep (lib/NVGPUKernels/GemmProfiler.cu:71-79), thinned to the useful ones.
+int split_candidates(int64_t k, int *out) {
+  const int num_kb = static_cast<int>((k + BK - 1) / BK);
+  const int limit = static_cast<int>(k / 128 < 16 ? k / 128 : 16);
+  int n = 0;
+  for (int sp : {1, 2, 3, 4, 6, 8, 12, 16})
+    if (sp == 1 || (sp <= limit && sp <= num_kb)) out[n++] = sp;
+  return n;
+}
 }  // namespace
 
-int tuned_row(int64_t m, int64_t n, int64_t k, int act) {
+bool tuned_choice(int64_t m, int64_t n, int64_t k, int act, int *row, int *split) {
   load_env_cache_once();
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
   auto it = g_tuned.find(TuneKey{m, n, k, act});
-  return it == g_tuned.end() ? 0 : it->second;
+  if (it == g_tuned.end()) return false;
+  if (row) *row = it->second.row;
+  if (split) *split = it->second.split;
+  return true;
 }
 
+int tuned_row(int64_t m, int64_t n, int64_t k, int act) {
+  int row = 0;
+  return tuned_choice(m, n, k, act, &row, nullptr) ? row : 0;
+}
+
+// Text lines "M N K activation row [split]" (split defaults to 1).
 int tune_cache_load(const char *path) {
   FILE *f = path ? std::fopen(path, "r") : nullptr;
   if (!f) return -1;
-  long long m, n, k;
-  int act, row, count = 0;
+  char line[256];
+  int count = 0;
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
-  while (std::fscanf(f, "%lld %lld %lld %d %d", &m, &n, &k, &act, &row) == 5) {
-    if (row >= 1 && row <= kNumTileRows) {
-      g_tuned[TuneKey{m, n, k, act}] = row;
+  while (std::fgets(line, sizeof(line), f)) {
+    long long m, n, k;
+    int act, row, split = 1;
+    const int got = std::sscanf(line, "%lld %lld %lld %d %d %d", &m, &n, &k, &act, &row, &split);
+    if (got >= 5 && row >= 1 && row <= kNumTileRows) {
+      if (got < 6 || split < 1) split = 1;
+      g_tuned[TuneKey{m, n, k, act}] = TuneChoice{row, split};
       ++count;
     }
   }
@@ -843,18 +938,21 @@ int tune_cache_save(const char *path) {
   if (!f) return -1;
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
   for (const auto &kv : g_tuned)
-    std::fprintf(f, "%lld %lld %lld %d %d\n", static_cast<long long>(std::get<0>(kv.first)),
+    std::fprintf(f, "%lld %lld %lld %d %d %d\n", static_cast<long long>(std::get<0>(kv.first)),
                  static_cast<long long>(std::get<1>(kv.first)),
-                 static_cast<long long>(std::get<2>(kv.first)), std::get<3>(kv.first), kv.second);
+                 static_cast<long long>(std::get<2>(kv.first)), std::get<3>(kv.first), kv.second.row,
+                 kv.second.split);
   std::fclose(f);
   return static_cast<int>(g_tuned.size());
 }
 
-// Times every row of the tile table on scratch buffers of the given shape (the contract of
-// GemmProfiler::profile, lib/NVGPUKernels/GemmProfiler.cu:143-236: warm up, then batches of
-// launches between two events on one stream; beta != 0 reads C = D like the reference does).
+// Times every row of the tile table, each with every candidate K split, on scratch buffers of
+// the given shape (the contract of GemmProfiler::profile, lib/NVGPUKernels/GemmProfiler.cu:
+// 143-236: warm up, then batches of launches between two events on one stream; a candidate that
+// is 1.2 x slower than the best so far after its warm-up batch is dropped early; beta != 0 reads
+// C = D like the reference does).  row_us[r - 1] is the best time of row r over its splits.
 bool tune(int64_t m, int64_t n, int64_t k, int act, float alpha, float beta, bool b_is_nk, int iters,
-          int *best_row, float *best_us, float *row_us, cudaStream_t stream) {
+          int *best_row, int *best_split, float *best_us, float *row_us, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || (!b_is_nk && n % 8 != 0)) {
     set_error(HOM_ERR_UNSUPPORTED, "homGemmTune: shape %lld x %lld x %lld is not supported",
               static_cast<long long>(m), static_cast<long long>(n), static_cast<long long>(k));
@@ -881,6 +979,7 @@ bool tune(int64_t m, int64_t n, int64_t k, int act, float alpha, float beta, boo
   fill_pattern_kernel<<<592, 256, 0, stream>>>(a, static_cast<size_t>(m) * k, 1u, 1.f);
   fill_pattern_kernel<<<592, 256, 0, stream>>>(b, static_cast<size_t>(k) * n, 2u, 0.03f);
   fill_pattern_kernel<<<592, 256, 0, stream>>>(d, static_cast<size_t>(m) * n, 3u, 0.5f);
+  declare_constant_range(b, sizeof(__half) * k * n);  // weights in the model: prefetched early
   Problem pb;
   pb.M = m;
   pb.N = n;
@@ -888,77 +987,154 @@ bool tune(int64_t m, int64_t n, int64_t k, int act, float alpha, float beta, boo
   pb.A = a;
   pb.B = b;
   pb.b_is_nk = b_is_nk;
+  pb.b_const = true;
   pb.C = beta != 0.f ? d : nullptr;
   pb.c_mode = beta != 0.f ? 1 : 0;
   pb.D = d;
   pb.alpha = alpha;
   pb.beta = beta;
   pb.act = act;
-  int best = 0;
+  int best = 0, best_sp = 1;
   float best_ms = 1e30f;
   bool ok = true;
+  int splits[8];
+  const int n_splits = split_candidates(k, splits);
   for (int row = 1; row <= kNumTileRows && ok; ++row) {
-    for (int i = 0; i < 3 && ok; ++i) ok = run(pb, row, stream);
-    if (!ok) break;
-    cudaEventRecord(e0, stream);
-    for (int i = 0; i < iters && ok; ++i) ok = run(pb, row, stream);
-    cudaEventRecord(e1, stream);
-    if (cudaEventSynchronize(e1) != cudaSuccess) ok = false;
-    float ms = 0.f;
-    if (ok) cudaEventElapsedTime(&ms, e0, e1);
-    const float us = 1e3f * ms / iters;
-    if (row_us) row_us[row - 1] = us;
-    if (ok && ms < best_ms) {
-      best_ms = ms;
-      best = row;
+    float row_best = 1e30f;
+    for (int si = 0; si < n_splits && ok; ++si) {
+      pb.split_k = splits[si];
+      auto timed = [&](int count, float *ms) {
+        cudaEventRecord(e0, stream);
+        for (int i = 0; i < count && ok; ++i) ok = run(pb, row, stream);
+        cudaEventRecord(e1, stream);
+        if (cudaEventSynchronize(e1) != cudaSuccess) ok = false;
+        *ms = 0.f;
+        if (ok) cudaEventElapsedTime(ms, e0, e1);
+      };
+      float warm_ms = 0.f, ms = 0.f;
+      timed(5, &warm_ms);
+      if (!ok) break;
+      if (warm_ms / 5 > 1.2f * best_ms) continue;  // early-out like the reference's profiler
+      timed(iters, &ms);
+      if (!ok) break;
+      ms /= iters;
+      if (ms < row_best) row_best = ms;
+      if (ms < best_ms) {
+        best_ms = ms;
+        best = row;
+        best_sp = splits[si];
+      }
     }
+    if (row_us) row_us[row - 1] = row_best < 1e29f ? 1e3f * row_best : -1.f;
   }
+  forget_constant_range(b);
   cleanup();
   if (!ok || best == 0) return false;
   {
     std::lock_guard<std::mutex> lock(g_tuned_mutex);
-    g_tuned[TuneKey{m, n, k, act}] = best;
+    g_tuned[TuneKey{m, n, k, act}] = TuneChoice{best, best_sp};
   }
   if (best_row) *best_row = best;
-  if (best_us) *best_us = 1e3f * best_ms / iters;
+  if (best_split) *best_split = best_sp;
+  if (best_us) *best_us = 1e3f * best_ms;
   return true;
 }
 
-int select_tile_row(int64_t m, int64_t n, int64_t k, int act) {
-  if (const char *env = std::getenv("HOM_GEMM_TILE")) {  // experiment knob
-    const int v = std::atoi(env);
-    if (v >= 1 && v <= kNumTileRows) return v;
-  }
-  if (const int row = tuned_row(m, n, k, act)) return row;
-  for (const ShapeRow &r : kShapeTable)
-    if (r.m == m && r.n == n && r.k == k && r.act == act) return r.row;
-  // Estimated time = waves x per-tile time.  A wave is 148 single-CTA tiles or 74 pair
-  // tiles; the per-tile time grows with the tile's N (MMA columns per K step) plus a fixed
-  // part, and a single CTA sustains a lower MMA rate than a pair (its TMA ring is shallower
-  // relative to the bytes it has to pull per K step).
+namespace {
+// Estimated duration (clock cycles) of a launch with tile-table row `row` and K split `sp`.
+//   per K block: the slower of the MMA time (N / 2 clocks per 16-deep MMA on one SM) and the
+//   time to pull the block's operand bytes through the L2 -> SM path (~70 B/clk/SM);
+//   per unit: its K blocks plus whatever of the previous unit's epilogue they do not hide;
+//   per launch: the ramp (set-up, first loads) and the last unit's epilogue; a split adds the
+//   partial write / read round of the fix-up.
+double estimate_cycles(int row, int sp, int64_t m, int64_t n, int64_t k, int act) {
+  const TileRow &t = kTileRows[row];
   const int sms = sm_count();
+  const int64_t tiles = ((m + t.tile_m - 1) / t.tile_m) * ((n + t.tile_n - 1) / t.tile_n);
+  const int64_t slots = t.pair ? sms / 2 : sms;
+  const int64_t num_kb = (k + BK - 1) / BK;
+  const int64_t units = tiles * sp;
+  const int64_t rounds = (units + slots - 1) / slots;
+  const double kb_unit = static_cast<double>((num_kb + sp - 1) / sp);
+  const double cols_per_sm = t.pair ? t.tile_n / 2.0 : t.tile_n;
+  const double bytes_kb = 128.0 * BK * 2 + cols_per_sm * BK * 2;
+  const double mma_kb = 4.0 * (t.tile_n < 128 ? 74.0 : t.tile_n / 2.0);
+  const double t_kb = std::max(mma_kb * 1.08, bytes_kb / 70.0);
+  const double t_epi = 1200.0 + (act ? 14.0 : 7.0) * t.tile_n;
+  const double t_unit = kb_unit * t_kb;
+  double cycles = 3000.0 + rounds * t_unit + (rounds - 1) * std::max(0.0, t_epi - t_unit) + t_epi;
+  // A split moves every unit's fp32 block through L2 once more per part (the same L2 -> SM
+  // path the operands use) and chains the parts' epilogues: measured 6-8 us per extra part at
+  // 256-wide tiles when the SMs are busy, so it only pays when most SMs would otherwise idle.
+  if (sp > 1) cycles += (sp - 1) * (3000.0 + 40.0 * cols_per_sm);
+  return cycles;
+}
+}  // namespace
+
+int select_split(int row, int64_t m, int64_t n, int64_t k, int act) {
+  if (row < 1 || row > kNumTileRows) return 1;
+  int splits[8];
+  const int n_splits = split_candidates(k, splits);
   int best = 1;
   double best_cost = 1e300;
-  for (int row = 1; row <= kNumTileRows; ++row) {
-    const TileRow &t = kTileRows[row];
-    const int64_t tiles = ((m + t.tile_m - 1) / t.tile_m) * ((n + t.tile_n - 1) / t.tile_n);
-    const int64_t slots = t.pair ? sms / 2 : sms;
-    const int64_t waves = (tiles + slots - 1) / slots;
-    const double per_tile = t.pair ? t.tile_n + 48.0 : 1.5 * t.tile_n + 48.0;
-    const double cost = static_cast<double>(waves) * per_tile;
-    if (cost < best_cost - 1e-9) {
-      best_cost = cost;
-      best = row;
+  for (int i = 0; i < n_splits; ++i) {
+    const double c = estimate_cycles(row, splits[i], m, n, k, act);
+    if (c < best_cost * 0.97) {  // a split has to pay for itself clearly
+      best_cost = c;
+      best = splits[i];
     }
   }
   return best;
 }
 
+int select_tile_row(int64_t m, int64_t n, int64_t k, int act, int *split_k) {
+  if (split_k) *split_k = 1;
+  HOM_DIAG(if (const char *env = std::getenv("HOM_GEMM_TILE")) {  // experiment knob
+    const int v = std::atoi(env);
+    if (v >= 1 && v <= kNumTileRows) {
+      if (split_k) *split_k = std::getenv("HOM_GEMM_SPLIT") ? std::atoi(std::getenv("HOM_GEMM_SPLIT")) : 1;
+      return v;
+    }
+  })
+  int row = 0, sp = 1;
+  if (tuned_choice(m, n, k, act, &row, &sp)) {
+    if (split_k) *split_k = sp;
+    return row;
+  }
+  for (const ShapeRow &r : kShapeTable)
+    if (r.m == m && r.n == n && r.k == k && r.act == act) {
+      if (split_k) *split_k = r.split;
+      return r.row;
+    }
+  int best = 1, best_sp = 1;
+  double best_cost = 1e300;
+  int splits[8];
+  const int n_splits = split_candidates(k, splits);
+  for (int r = 1; r <= kNumTileRows; ++r) {
+    const TileRow &t = kTileRows[r];
+    const int64_t tiles = ((m + t.tile_m - 1) / t.tile_m) * ((n + t.tile_n - 1) / t.tile_n);
+    const int64_t slots = t.pair ? sm_count() / 2 : sm_count();
+    for (int i = 0; i < n_splits; ++i) {
+      // split only a problem that leaves at least half of the SMs idle and has a long K
+      if (splits[i] > 1 && (2 * tiles > slots || k < 2048)) continue;
+      double c = estimate_cycles(r, splits[i], m, n, k, act);
+      if (c < best_cost - 1e-9) {
+        best_cost = c;
+        best = r;
+        best_sp = splits[i];
+      }
+    }
+  }
+  if (split_k) *split_k = best_sp;
+  return best;
+}
+
 int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, int *split_k) {
-  const int row = select_tile_row(m, n, k, act);
+  int sp = 1;
+  const int row = select_tile_row(m, n, k, act, &sp);
   if (bn) *bn = kTileRows[row].tile_n;
   if (stages) *stages = kTileRows[row].stages;
-  if (split_k) *split_k = 1;
+  if (split_k) *split_k = sp;
   return row;
 }
 
@@ -1002,22 +1178,28 @@ bool run_layernorm_fused(const Problem &pb, float eps, cudaStream_t stream) {
 
 bool run(const Problem &pb, int tile_row, cudaStream_t stream) {
   if (pb.M == 0 || pb.N == 0) return true;
-  if (tile_row < 1 || tile_row > kNumTileRows) tile_row = select_tile_row(pb.M, pb.N, pb.K, pb.act);
+  int split = 1;
+  if (tile_row < 1 || tile_row > kNumTileRows) {
+    tile_row = select_tile_row(pb.M, pb.N, pb.K, pb.act, &split);
+    if (pb.split_k >= 2) split = pb.split_k;
+  } else {
+    split = pb.split_k >= 2 ? pb.split_k : 1;
+  }
   const TileRow &t = kTileRows[tile_row];
-  if (t.pair) return run_pair(pb, t.tile_n, stream);
+  if (t.pair) return run_pair(pb, t.tile_n, split, stream);
   if (pb.b_is_nk) {
     switch (t.tile_n) {
-      case 64: return launch_variant<64, true>(pb, stream);
-      case 128: return launch_variant<128, true>(pb, stream);
-      case 192: return launch_variant<192, true>(pb, stream);
-      default: return launch_variant<256, true>(pb, stream);
+      case 64: return launch_variant<64, true>(pb, split, stream);
+      case 128: return launch_variant<128, true>(pb, split, stream);
+      case 192: return launch_variant<192, true>(pb, split, stream);
+      default: return launch_variant<256, true>(pb, split, stream);
     }
   }
   switch (t.tile_n) {
-    case 64: return launch_variant<64, false>(pb, stream);
-    case 128: return launch_variant<128, false>(pb, stream);
-    case 192: return launch_variant<192, false>(pb, stream);
-    default: return launch_variant<256, false>(pb, stream);
+    case 64: return launch_variant<64, false>(pb, split, stream);
+    case 128: return launch_variant<128, false>(pb, split, stream);
+    case 192: return launch_variant<192, false>(pb, split, stream);
+    default: return launch_variant<256, false>(pb, split, stream);
   }
 }
 

@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include "hom_common.cuh"
+#include "hom_diag.cuh"
 
 namespace hom {
 namespace gemm {
@@ -13,11 +14,17 @@ struct Problem {
   const __half *A = nullptr;    // [M, K]
   const __half *B = nullptr;    // [K, N], or [N, K] when b_is_nk
   bool b_is_nk = false;
+  // B lies in a declared constant range: its first tiles may be requested before the previous
+  // kernel of the stream has finished.
+  bool b_const = false;
   const __half *C = nullptr;
   int c_mode = 0;  // 0 none, 1 full [M, N] (may alias D), 2 length-N row broadcast
   __half *D = nullptr;
   float alpha = 1.f, beta = 0.f;
   int act = 0;  // 1 = erf GELU
+  // K parts per output tile: >= 2 as given (clamped to the number of 64-wide K blocks and 16),
+  // anything else lets the tile table / tuner / heuristic decide.
+  int split_k = 0;
   // LayerNorm-on-A form (all null when unused): D = epilogue(alpha * (A * row_scale + row_shift).B ...)
   // evaluated as row_scale[r] * (A.B)[r,n] + row_shift[r] * col_sum[n] with col_sum = column sums of B.
   const __half *row_scale = nullptr;
@@ -36,28 +43,35 @@ bool run(const Problem &pb, int tile_row, cudaStream_t stream);
 bool run_layernorm_fused(const Problem &pb, float eps, cudaStream_t stream);
 bool layernorm_fusion_shape(int64_t n, int *cluster_n, int *bn);
 // The CTA-pair kernels (gemm_pair_sm100.cu); bn2 is 128 or 256.
-bool run_pair(const Problem &pb, int bn2, cudaStream_t stream);
+bool run_pair(const Problem &pb, int bn2, int split_k, cudaStream_t stream);
 
 // The 128 x 128 single-CTA kernel for `pb` (B as [K, N]) launched without any allocation (no
 // tensor-map cache insert, no status-word creation).
 bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream);
 
-int select_tile_row(int64_t m, int64_t n, int64_t k, int act);
+// Tile-table row and K split for a shape (tuned entry, else table, else cost heuristic).
+int select_tile_row(int64_t m, int64_t n, int64_t k, int act, int *split_k = nullptr);
+// Split the heuristic would use for a given row.
+int select_split(int row, int64_t m, int64_t n, int64_t k, int act);
 int query_tile(int64_t m, int64_t n, int64_t k, int act, int *bn, int *stages, int *split_k);
 
-// Diagnostics, enabled by HOM_GEMM_PROFILE=1 only: per-role cycle counters of CTA 0.
 // Run-time tuner (GemmProfiler's contract): times the tile-table rows for one shape, remembers
 // the winner for later automatic selections, and can persist the table as text.
 bool tune(int64_t m, int64_t n, int64_t k, int act, float alpha, float beta, bool b_is_nk, int iters,
-          int *best_row, float *best_us, float *row_us, cudaStream_t stream);
+          int *best_row, int *best_split, float *best_us, float *row_us, cudaStream_t stream);
 int tuned_row(int64_t m, int64_t n, int64_t k, int act);
+bool tuned_choice(int64_t m, int64_t n, int64_t k, int act, int *row, int *split);
 int tune_cache_load(const char *path);  // entries read, or -1
 int tune_cache_save(const char *path);  // entries written, or -1
 
+#if HOM_DIAG_ENABLED
+// Diagnostics builds only (HOM_GEMM_PROFILE=1): per-role cycle counters of CTA 0 and launch
+// timelines in a small device buffer.
 long long *profile_buffer();
 long long *profile_buffer_raw();  // the buffer if it exists; touches nothing
-long long *launch_timeline_slot();  // diagnostics: where this launch stamps its CTA entry/exit times
+long long *launch_timeline_slot();  // where this launch stamps its CTA entry/exit times
 void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStream_t stream);
+#endif
 
 // Cached cuTensorMapEncodeTiled for a 2-D fp16 tensor [outer, inner], 128-byte swizzle.
 bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,

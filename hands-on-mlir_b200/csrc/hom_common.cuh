@@ -73,6 +73,11 @@ enum OpKind : int32_t {
 };
 
 cudaStream_t current_stream();
+// Registry of device ranges that no kernel writes (allocConstantNVGPU* buffers and ranges
+// named through homDeclareWeights).
+void declare_constant_range(const void *ptr, size_t bytes);
+void forget_constant_range(const void *ptr);
+bool is_constant_range(const void *ptr, size_t bytes);
 // Programmatic dependent launch is on unless HOM_DISABLE_PDL is set (diagnostics).
 bool pdl_enabled();
 // Host-mapped status word that device code writes on a bounded-wait expiry (device pointer).
@@ -81,6 +86,20 @@ int *device_status_word();
 // allocates.
 int *device_status_word_if_ready();
 int sm_count();
+
+// Library-owned split-K scratch of the calling host thread for (current device, `stream`):
+// `slot_floats` fp32 values of partial accumulators and `blocks` int counters that are zero
+// whenever no GEMM is in flight.  Grow-only, allocated on first use (the reference keeps
+// grow-only static device scratch for its split-K semaphores too,
+// include/NVGPUKernels/Utils.h:179-224); growing it, or re-zeroing the counters after a kernel
+// reported an expired wait, synchronises the device.  Returns false (error recorded) on failure.
+struct SplitWorkspace {
+  float *slots = nullptr;
+  int *counters = nullptr;
+};
+bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, SplitWorkspace *out);
+// Called when a kernel reported an expired wait: counters may have been left non-zero.
+void split_workspace_mark_dirty();
 
 // Launches `kernel` with programmatic stream serialization allowed (and, when cluster_x > 1,
 // as clusters of that many CTAs along x).  Every kernel of this library calls
@@ -115,7 +134,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 blo
 // records events on the current stream.
 class LaunchScope {
  public:
-  LaunchScope(OpKind kind, double flops, double bytes);
+  // `may_allocate` false: only count the launch, even while per-launch timing is enabled
+  // (timing creates events and grows a host vector).
+  LaunchScope(OpKind kind, double flops, double bytes, bool may_allocate = true);
   ~LaunchScope();
 
  private:

@@ -8,6 +8,8 @@
 // in a buffer it cudaMallocs on first use; this one keeps it in a fixed array that is part of
 // the loaded library image, so the only memory it ever touches is the caller's tensors and
 // that array.
+#include <atomic>
+
 #include "bandwidth_kernels.cuh"
 #include "gemm_sm100.cuh"
 #include "hom_common.cuh"
@@ -37,21 +39,24 @@ col_sum_into_scratch_kernel(const __half *b, float *out, int k_dim, int n_dim) {
 
 // Device address of the scratch array on the current device, looked up once per device.
 float *scratch_address() {
-  static float *addr[64] = {};
+  static std::atomic<float *> addr[64] = {};
   int dev = 0;
   if (!hom::check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return nullptr;
   if (dev < 0 || dev >= 64) {
     hom::set_error(HOM_ERR_UNSUPPORTED, "homLayernormGemmF16NoAlloc: device index %d out of range", dev);
     return nullptr;
   }
-  if (!addr[dev]) {
+  float *cached = addr[dev].load(std::memory_order_acquire);
+  if (!cached) {
+    // Host threads that race here all look up the same address; the last store wins harmlessly.
     void *ptr = nullptr;
     if (!hom::check_cuda(cudaGetSymbolAddress(&ptr, g_col_sum_scratch),
                          "cudaGetSymbolAddress(column-sum scratch)"))
       return nullptr;
-    addr[dev] = static_cast<float *>(ptr);
+    cached = static_cast<float *>(ptr);
+    addr[dev].store(cached, std::memory_order_release);
   }
-  return addr[dev];
+  return cached;
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -106,7 +111,8 @@ extern "C" __attribute__((visibility("default"))) void homLayernormGemmF16NoAllo
   pb.alpha = alpha;
   pb.beta = beta;
   if (beta != 0.f) {
-    if (!C.valid || !C.contiguous() || !(C.numel() == M * N || C.numel() == N)) {
+    if (!C.valid || !C.contiguous() || C.rank < 1 || C.sizes[C.rank - 1] != N ||
+        !(C.numel() == M * N || C.numel() == N)) {
       set_error(HOM_ERR_INVALID, "%s: beta != 0 needs C of shape [Bs,M,N] or [1,1,N]", name);
       return;
     }
@@ -121,7 +127,7 @@ extern "C" __attribute__((visibility("default"))) void homLayernormGemmF16NoAllo
   if (!scratch) return;
   cudaStream_t stream = hom::current_stream();
   {
-    hom::LaunchScope scope(hom::kOpElementwise, 0.0, 2.0 * K * N + 4.0 * N);
+    hom::LaunchScope scope(hom::kOpElementwise, 0.0, 2.0 * K * N + 4.0 * N, /*may_allocate=*/false);
     // Entries [0, N) are rewritten here on every call before the GEMM reads them, so nothing
     // left over from an earlier call (or from a larger N) is ever consumed.
     if (!hom::check_cuda(hom::launch_pdl(col_sum_into_scratch_kernel, dim3(static_cast<unsigned>((N + 255) / 256)),

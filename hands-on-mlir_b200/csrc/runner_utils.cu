@@ -215,6 +215,7 @@ HomUnrankedMemRef alloc_constant(int32_t idx) {
   if (!res.descriptor) return res;
   void *data = static_cast<void **>(res.descriptor)[1];
   if (!data) return res;
+  hom::declare_constant_range(data, values.size() * sizeof(T));
   if (sizeof(T) == 2) {
     std::vector<__half> h(values.size());
     for (size_t i = 0; i < values.size(); ++i) h[i] = __float2half_rn(values[i]);
@@ -231,6 +232,7 @@ void dealloc_memref(int64_t rank, void *dst) {
   if (!dst) return;
   void *data = static_cast<void **>(dst)[1];
   (void)rank;
+  hom::forget_constant_range(data);
   if (data) hom::check_cuda(cudaFree(data), "cudaFree");
 }
 
@@ -311,6 +313,7 @@ bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int
   pb.A = reinterpret_cast<const __half *>(A.ptr);
   pb.B = reinterpret_cast<const __half *>(B.ptr);
   pb.b_is_nk = b_is_nk;
+  pb.b_const = hom::is_constant_range(B.ptr, static_cast<size_t>(K) * N * 2);
   pb.D = reinterpret_cast<__half *>(D.ptr);
   pb.alpha = alpha;
   pb.beta = beta;
@@ -347,12 +350,13 @@ bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int
 // Shared front end of cutlassGemmF16 / nvteGemmF16.
 void gemm_entry(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64_t rankB,
                 void *dstB, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
-                int64_t activation, float alpha, float beta, int32_t tile_row) {
+                int64_t activation, float alpha, float beta, int32_t tile_row, int32_t split_k) {
   hom::gemm::Problem pb;
   bool empty = false;
   if (!gemm_prepare(name, b_is_nk, rankA, dstA, rankB, dstB, rankC, dstC, rankD, dstD, activation,
                     alpha, beta, &pb, &empty))
     return;
+  pb.split_k = split_k;
   hom::gemm::run(pb, tile_row, hom::current_stream());
 }
 
@@ -504,12 +508,13 @@ void cutlassGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void 
                     int64_t rankC, void *dstC, int64_t rankD, void *dstD, int64_t activation,
                     float alpha, float beta, int32_t gemmNum, int32_t splitKFactor) {
   // Like the reference entry point, the transpose flags are not consulted: A is [.,M,K] and
-  // B is [1,K,N].  splitKFactor is accepted as a hint; the tile table decides.
+  // B is [1,K,N].  splitKFactor >= 2 cuts every output tile's K range into that many work
+  // units (include/NVGPUKernels/GemmRunner.h:279-284 hands the factor to the kernel the same
+  // way); the default 1 that un-tuned models pass leaves the choice to the tile table.
   (void)transa;
   (void)transb;
-  (void)splitKFactor;
   gemm_entry("cutlassGemmF16", false, rankA, dstA, rankB, dstB, rankC, dstC, rankD, dstD,
-             activation, alpha, beta, gemmNum);
+             activation, alpha, beta, gemmNum, splitKFactor);
 }
 
 void cutlassGemmF32(int64_t, void *, bool, int64_t, void *, bool, int64_t, void *, int64_t, void *,
@@ -531,7 +536,7 @@ void nvteGemmF16(int64_t rankA, void *dstA, bool transa, int64_t rankB, void *ds
     return;
   }
   gemm_entry("nvteGemmF16", true, rankA, dstA, rankB, dstB, rankC, dstC, rankD, dstD, activation,
-             alpha, beta, gemmNum);
+             alpha, beta, gemmNum, 0);
 }
 
 void cutlassGemmWithVarMeanF16(int64_t rankA, void *dstA, int64_t rankB, void *dstB, int64_t rankC,
@@ -832,6 +837,7 @@ void printMemrefSizeF16(int64_t rank, void *d) { print_sizes(rank, d); }
 void printMemrefSizeI64(int64_t rank, void *d) { print_sizes(rank, d); }
 void printMemrefSizeI32(int64_t rank, void *d) { print_sizes(rank, d); }
 
+#if HOM_DIAG_ENABLED
 // Diagnostics only (HOM_GEMM_PROFILE=1 HOM_GEMM_TIMELINE=1): copies the 64-word profile buffer.
 __attribute__((visibility("default"))) void homDebugReadGemmProfile(long long *out) {
   long long *buf = hom::gemm::profile_buffer();
@@ -844,6 +850,7 @@ __attribute__((visibility("default"))) void homDebugReadProfile(long long *out, 
   cudaDeviceSynchronize();
   if (buf && count > 0 && count <= 4096) cudaMemcpy(out, buf, count * sizeof(long long), cudaMemcpyDeviceToHost);
 }
+#endif  // HOM_DIAG_ENABLED
 
 void homSetConstantCache(int enable) { g_constant_cache.store(enable ? 1 : 0); }
 
@@ -870,13 +877,13 @@ int32_t homGemmTune(int64_t m, int64_t n, int64_t k, int64_t activation, float a
                    static_cast<long long>(activation));
     return HOM_ERR_UNSUPPORTED;
   }
-  int row = 0;
+  int row = 0, split = 1;
   float us = 0.f;
   if (!hom::gemm::tune(m, n, k, static_cast<int>(activation), alpha, beta, weights_nk != 0, iterations,
-                       &row, &us, row_us, hom::current_stream()))
+                       &row, &split, &us, row_us, hom::current_stream()))
     return homGetLastError() ? homGetLastError() : HOM_ERR_CUDA;
   if (tile_row) *tile_row = row;
-  if (split_k) *split_k = 1;
+  if (split_k) *split_k = split;
   if (best_us) *best_us = us;
   return 0;
 }

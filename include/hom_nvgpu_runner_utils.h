@@ -181,6 +181,18 @@ HOM_EXPORT void *homGetStream(void);
  * Returns the error code. */
 HOM_EXPORT int homSynchronize(void);
 
+/* Declares that no kernel will write [ptr, ptr + bytes) while GEMMs read it as their B operand
+ * (model weights).  Kernels of this library are launched so that one may start while the previous
+ * kernel of the stream is still finishing; a GEMM requests its first tiles of a DECLARED B before
+ * that previous kernel is known to be complete, and those of any other B only afterwards, so a B
+ * that an earlier call on the stream produced is always read after it was written.  Buffers
+ * returned by allocConstantNVGPU* are declared by the library; callers that bring their own
+ * weight buffers may declare them to get the earlier prefetch.  homForgetWeights() withdraws a
+ * declaration (call it before the buffer is freed or reused).  No counterpart in the reference,
+ * whose launches are fully serialised on the null stream. */
+HOM_EXPORT void homDeclareWeights(const void *ptr, int64_t bytes);
+HOM_EXPORT void homForgetWeights(const void *ptr);
+
 /* Directory that allocConstantNVGPU* reads "<idx>.txt" from (default: $HOM_CONSTANT_DIR,
  * else the current directory). */
 HOM_EXPORT void homSetConstantDir(const char *dir);
@@ -235,7 +247,10 @@ HOM_EXPORT void homResidualLayernormF16(int64_t rankX, void *dstX, int64_t rankR
  * array: each call rewrites the entries it uses before reading them, so nothing needs
  * clearing between calls, but two calls whose kernels overlap on the GPU (different streams,
  * or host threads on one device) would overwrite each other's sums - issue them on one stream.
- * This entry point has no counterpart in the reference. */
+ * Its launches are counted but never timed by homOpTimingEnable (timing allocates events), and
+ * an expired device-side wait is reported by homSynchronize() only if some other entry point of
+ * this library has run on the device before (that is what creates the status word; this one
+ * will not allocate it).  This entry point has no counterpart in the reference. */
 HOM_EXPORT void homLayernormGemmF16NoAlloc(int64_t rankA, void *dstA, int64_t rankB, void *dstB,
                                            int64_t rankC, void *dstC, int64_t rankD, void *dstD,
                                            int64_t rankVar, void *dstVar, int64_t rankMean,

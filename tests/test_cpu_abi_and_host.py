@@ -135,14 +135,17 @@ def test_tuned_table_round_trips_through_a_cache_file(hom, tmp_path):
     """The tuned table (the stand-in for GemmProfiler's timing cache) overrides the built-in
     choice, and what is saved is what is loaded."""
     src = tmp_path / "tuned.txt"
-    src.write_text("1000 520 264 0 2\n1000 520 264 1 5\n77 8 8 0 9\n")  # row 9 is not a table row
+    # "M N K activation row [split]"; a line without the split means 1; row 9 is not a table row
+    src.write_text("1000 520 264 0 2\n1000 520 264 1 5 3\n77 8 8 0 9\n")
     assert hom.gemm_tune_load(src) == 2
-    assert hom.gemm_query_tile(1000, 520, 264, 0)["row"] == 2
-    assert hom.gemm_query_tile(1000, 520, 264, 1)["row"] == 5
+    q = hom.gemm_query_tile(1000, 520, 264, 0)
+    assert (q["row"], q["split_k"]) == (2, 1)
+    q = hom.gemm_query_tile(1000, 520, 264, 1)
+    assert (q["row"], q["split_k"]) == (5, 3)
     out = tmp_path / "saved.txt"
     assert hom.gemm_tune_save(out) >= 2
     lines = {tuple(map(int, l.split())) for l in out.read_text().splitlines()}
-    assert (1000, 520, 264, 0, 2) in lines and (1000, 520, 264, 1, 5) in lines
+    assert (1000, 520, 264, 0, 2, 1) in lines and (1000, 520, 264, 1, 5, 3) in lines
     assert hom.gemm_tune_load(tmp_path / "missing.txt") == -1
 
 

@@ -194,3 +194,52 @@ def test_encoder_composition_matches_torch_fp32(oracle):
     want = x.numpy()
     for b, n in enumerate(lens):  # the reference compares valid tokens only
         assert_close_f16(got[b, :n], want[b, :n], f"encoder seq {b}", rtol=1e-2, atol=1e-2)
+
+
+def test_encoder_composition_matches_huggingface_bert_model(oracle):
+    """The oracle's encoder against the model class the reference exports
+    (examples/torch/bert/convert_hf.py:44-45 builds a Hugging Face BERT and lowers it): a
+    randomly initialised `BertModel` in fp32 with its weights rounded to fp16 and handed to the
+    oracle in the layout the lowering produces (Wq|Wk|Wv concatenated along the output
+    dimension, lib/Conversions/HOM/HOMFusionPass.cpp:317-346).  Pins the embedding order, the
+    position ids, the post-LayerNorm placement and the packed-QKV head order.  Valid tokens
+    only, tolerance 1e-2 as in the reference's end-to-end check (bert.cu:148-153)."""
+    import torch
+    transformers = pytest.importorskip("transformers")
+    L, H, heads, F, V, S, B = 2, 128, 2, 256, 60, 64, 3
+    cfg = transformers.BertConfig(vocab_size=V, hidden_size=H, num_hidden_layers=L, num_attention_heads=heads,
+                                  intermediate_size=F, max_position_embeddings=S, type_vocab_size=2,
+                                  hidden_act="gelu", layer_norm_eps=1e-12, hidden_dropout_prob=0.0,
+                                  attention_probs_dropout_prob=0.0)
+    torch.manual_seed(3)
+    model = transformers.BertModel(cfg, add_pooling_layer=False).eval()
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if name.endswith("LayerNorm.weight"):
+                prm.fill_(1.0)
+            elif name.endswith(".bias"):
+                prm.zero_()  # the lowered model has neither biases nor LayerNorm affine
+            else:
+                prm.copy_(prm.half().float())  # both sides see the same fp16 weights
+    sd = {k: v.detach().numpy() for k, v in model.state_dict().items()}
+    w = {"word_emb": f16(sd["embeddings.word_embeddings.weight"][None]),
+         "pos_emb": f16(sd["embeddings.position_embeddings.weight"][None]),
+         "type_emb": f16(sd["embeddings.token_type_embeddings.weight"][None])}
+    for i in range(L):
+        pre = f"encoder.layer.{i}."
+        wq, wk, wv = (sd[pre + f"attention.self.{n}.weight"].T for n in ("query", "key", "value"))
+        w[f"wqkv_{i}"] = f16(np.concatenate([wq, wk, wv], axis=1)[None])
+        w[f"wo_{i}"] = f16(sd[pre + "attention.output.dense.weight"].T[None])
+        w[f"w1_{i}"] = f16(sd[pre + "intermediate.dense.weight"].T[None])
+        w[f"w2_{i}"] = f16(sd[pre + "output.dense.weight"].T[None])
+    rng = np.random.Generator(np.random.PCG64(21))
+    lens = np.array([64, 40, 17])
+    ids = rng.integers(0, V, (B, S)).astype(np.int64)
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.int64)
+    types = rng.integers(0, 2, (B, S)).astype(np.int64)
+    got = oracle.bert_encoder(w, ids, mask, types, heads=heads, eps=1e-12).astype(np.float32)
+    with torch.no_grad():
+        want = model(input_ids=torch.from_numpy(ids), attention_mask=torch.from_numpy(mask),
+                     token_type_ids=torch.from_numpy(types)).last_hidden_state.numpy()
+    for b, n in enumerate(lens):
+        assert_close_f16(got[b, :n], want[b, :n], f"HF BertModel seq {b}", rtol=1e-2, atol=1e-2)

@@ -18,7 +18,7 @@ def _rng(seed):
 
 # ------------------------------------------------------------------------ GEMM
 
-def _run_gemm(hom, dev, A, B, C, *, nk=False, act=0, alpha=1.0, beta=0.0, tile=0, alias=False):
+def _run_gemm(hom, dev, A, B, C, *, nk=False, act=0, alpha=1.0, beta=0.0, tile=0, alias=False, split=1):
     import torch
     tA, tB = to_dev(A, dev), to_dev(B, dev)
     n = B.shape[-2] if nk else B.shape[-1]
@@ -31,7 +31,8 @@ def _run_gemm(hom, dev, A, B, C, *, nk=False, act=0, alpha=1.0, beta=0.0, tile=0
     if nk:
         hom.nvteGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta, gemmNum=tile)
     else:
-        hom.cutlassGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta, gemmNum=tile)
+        hom.cutlassGemmF16(tA, tB, tC, tD, activation=act, alpha=alpha, beta=beta, gemmNum=tile,
+                           splitKFactor=split)
     hom.synchronize()
     return tD.cpu().numpy()
 
@@ -67,6 +68,66 @@ def test_gemm_residual_aliases_output(hom, cuda, oracle, tile):
     C = rng.normal(0, 1, (2, 128, 768)).astype(np.float16)
     got = _run_gemm(hom, cuda, A, B, C, beta=1.0, alias=True, tile=tile)
     assert_close_f16(got, oracle.gemm_f16(A, B, C, beta=1.0), "residual C==D")
+
+
+# Split-K (the reference hands splitKFactor to its kernels, include/NVGPUKernels/GemmRunner.h:
+# 279-284, and its profiler sweeps 1..min(16, K/128), lib/NVGPUKernels/GemmProfiler.cu:71-79).
+# The reduction order differs from the unsplit kernel's, so every case is checked against the
+# oracle, never against split 1.
+@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("split", [2, 3, 4, 6, 8, 16])
+def test_gemm_split_k_every_factor_and_tile(hom, cuda, oracle, tile, split):
+    rng = _rng(40 + split)
+    bs, m, n, k = 2, 200, 328, 1024 + 64 * (split % 3)  # M and N tails, K blocks not divisible by every split
+    A = rng.uniform(-1, 1, (bs, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.03, (1, k, n)).astype(np.float16)
+    C = rng.normal(0, 1, (bs, m, n)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, C, beta=1.0, alias=True, tile=tile, split=split)
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, beta=1.0), f"split {split} tile {tile} residual C==D")
+    got = _run_gemm(hom, cuda, A, B, None, act=1, tile=tile, split=split)
+    assert_close_f16(got, oracle.gemm_f16(A, B, act=1), f"split {split} tile {tile} GELU")
+
+
+@pytest.mark.parametrize("split", [2, 3, 5])
+def test_gemm_split_k_more_parts_than_k_blocks_and_bias(hom, cuda, oracle, split):
+    """K = 128 has two 64-wide K blocks: larger factors are clamped; bias row broadcast."""
+    rng = _rng(50)
+    A = rng.uniform(-1, 1, (1, 384, 128)).astype(np.float16)
+    B = rng.normal(0, 0.05, (1, 128, 512)).astype(np.float16)
+    bias = rng.uniform(-1, 1, (1, 1, 512)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, bias, beta=1.0, act=1, split=split, tile=6)
+    assert_close_f16(got, oracle.gemm_f16(A, B, bias, beta=1.0, act=1), f"split {split} bias")
+
+
+def test_gemm_split_k_is_deterministic_and_leaves_its_counters_clean(hom, cuda, oracle):
+    """The serial in-order reduction gives the same bits every run, and a launch leaves the
+    workspace counters at zero so that the next launch - another shape and factor - is right."""
+    rng = _rng(51)
+    A = rng.normal(0, 1, (1, 1024, 3072)).astype(np.float16)
+    B = rng.normal(0, 0.02, (1, 3072, 768)).astype(np.float16)
+    C = rng.normal(0, 1, (1, 1024, 768)).astype(np.float16)
+    want = oracle.gemm_f16(A, B, C, beta=1.0)
+    first = _run_gemm(hom, cuda, A, B, C, beta=1.0, tile=6, split=3)
+    assert_close_f16(first, want, "FFN2-like split 3")
+    for _ in range(3):
+        again = _run_gemm(hom, cuda, A, B, C, beta=1.0, tile=6, split=3)
+        assert_bits_equal(again, first, "split-K repeat")
+    other = _run_gemm(hom, cuda, A[:, :300], B, None, tile=3, split=4)
+    assert_close_f16(other, oracle.gemm_f16(A[:, :300], B), "another shape after a split launch")
+
+
+def test_gemm_small_batch_ffn2_default_choice_uses_a_split(hom, cuda, oracle):
+    """128 x 768 x 3072 with the residual (FFN2 at batch 1 x seq 128): so few output tiles that
+    the library cuts K by itself; the BERT-base batch-32 shape stays unsplit (the partial sums
+    would travel the same L2 path that already limits it)."""
+    assert hom.gemm_query_tile(128, 768, 3072, 0)["split_k"] >= 2
+    assert hom.gemm_query_tile(4096, 768, 3072, 0)["split_k"] == 1
+    rng = _rng(52)
+    A = rng.normal(0, 1, (1, 128, 3072)).astype(np.float16)
+    B = rng.normal(0, 0.02, (1, 3072, 768)).astype(np.float16)
+    C = rng.normal(0, 1, (1, 128, 768)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, C, beta=1.0, alias=True)
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, beta=1.0), "FFN2 batch 1, default choice")
 
 
 def test_gemm_alpha_beta_gelu(hom, cuda, oracle):
@@ -341,9 +402,12 @@ def test_gemm_tuner_picks_a_row_and_later_calls_use_it(hom, cuda, oracle, tmp_pa
     remembered for automatic selection; results do not depend on the row."""
     m, n, k = 384, 520, 264
     res = hom.gemm_tune(m, n, k, activation=1, alpha=1.0, beta=0.0, iterations=5)
-    assert 1 <= res["row"] <= 6 and res["split_k"] == 1
-    assert all(t > 0 for t in res["row_us"]) and abs(min(res["row_us"]) - res["best_us"]) < 1e-3
-    assert hom.gemm_query_tile(m, n, k, 1)["row"] == res["row"]
+    assert 1 <= res["row"] <= 6 and res["split_k"] in (1, 2)  # K / 128 = 2 bounds the sweep
+    timed = [t for t in res["row_us"] if t > 0]  # rows dropped by the 1.2 x early-out report -1
+    assert timed and abs(min(timed) - res["best_us"]) < 1e-3
+    assert abs(res["row_us"][res["row"] - 1] - res["best_us"]) < 1e-3
+    q = hom.gemm_query_tile(m, n, k, 1)
+    assert (q["row"], q["split_k"]) == (res["row"], res["split_k"])
     assert hom.gemm_tune_save(tmp_path / "t.txt") >= 1
     rng = _rng(5)
     A = rng.uniform(-1, 1, (1, m, k)).astype(np.float16)
@@ -352,6 +416,23 @@ def test_gemm_tuner_picks_a_row_and_later_calls_use_it(hom, cuda, oracle, tmp_pa
     assert_close_f16(got, oracle.gemm_f16(A, B, act=1), "GEMM after tuning")
     with pytest.raises(Exception):
         hom.gemm_tune(m, n, 263, activation=0)  # K % 8 != 0 is rejected, nothing is launched
+
+
+def test_gemm_tuner_sweeps_the_k_split(hom, cuda, oracle):
+    """Long K and few output tiles: the sweep covers splits up to min(16, K / 128) like the
+    reference's profiler (lib/NVGPUKernels/GemmProfiler.cu:71-79, 186-222); whatever wins is
+    used by later calls and gives the oracle's result."""
+    m, n, k = 128, 768, 3072
+    res = hom.gemm_tune(m, n, k, activation=0, alpha=1.0, beta=1.0, iterations=5)
+    assert 1 <= res["row"] <= 6 and 1 <= res["split_k"] <= 16
+    q = hom.gemm_query_tile(m, n, k, 0)
+    assert (q["row"], q["split_k"]) == (res["row"], res["split_k"])
+    rng = _rng(6)
+    A = rng.normal(0, 1, (1, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.02, (1, k, n)).astype(np.float16)
+    C = rng.normal(0, 1, (1, m, n)).astype(np.float16)
+    got = _run_gemm(hom, cuda, A, B, C, beta=1.0, alias=True)
+    assert_close_f16(got, oracle.gemm_f16(A, B, C, beta=1.0), "GEMM after tuning with a split")
 
 
 def test_alloc_and_constant_loader(hom, cuda, oracle, tmp_path):

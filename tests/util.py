@@ -65,3 +65,43 @@ def drift_fractions(got, want):
     err, mag = np.abs(got - want), np.abs(want)
     return (float(np.mean(err > 1e-3 + 1e-3 * mag)), float(np.mean(err > 2e-3 + 2e-3 * mag)),
             float(np.mean((err > 1e-2) & (err > 1e-2 * mag))))
+
+
+def encoder_fp64(weights, input_ids, attention_mask, token_type_ids, *, heads, eps=1e-12, layers=None,
+                 return_layers=False):
+    """The encoder in float64 with no intermediate rounding at all (weights and embeddings are
+    the given fp16 values): the mathematical result both fp16 pipelines approximate.  Same op
+    order as the oracle's `bert_encoder`; padded key columns are excluded from the softmax and
+    padded query rows come back as zeros."""
+    from scipy.special import erf
+    ids = np.asarray(input_ids)
+    bs, seq = ids.shape
+    mask = np.asarray(attention_mask).astype(bool)
+    w = {k: np.asarray(v).astype(np.float64) for k, v in weights.items()}
+
+    def ln(z):
+        mu = z.mean(-1, keepdims=True)
+        var = ((z - mu) ** 2).mean(-1, keepdims=True)
+        return (z - mu) / np.sqrt(var + eps)
+
+    x = ln(w["word_emb"][0][ids] + w["type_emb"][0][np.asarray(token_type_ids)] + w["pos_emb"][0][None, :seq])
+    n_layers = layers if layers is not None else sum(1 for k in w if k.startswith("wqkv_"))
+    hidden = x.shape[-1]
+    d = hidden // heads
+    outs = []
+    for i in range(n_layers):
+        qkv = (x @ w[f"wqkv_{i}"][0]).reshape(bs, seq, 3, heads, d)
+        q, k, v = (qkv[:, :, j].transpose(0, 2, 1, 3) for j in range(3))
+        s = q @ k.transpose(0, 1, 3, 2) / np.sqrt(d)
+        s = np.where(mask[:, None, None, :], s, -np.inf)
+        s = s - s.max(-1, keepdims=True)
+        p = np.exp(s)
+        p /= p.sum(-1, keepdims=True)
+        ctx = (p @ v).transpose(0, 2, 1, 3).reshape(bs, seq, hidden) * mask[:, :, None]
+        y = ln(ctx @ w[f"wo_{i}"][0] + x)
+        h = y @ w[f"w1_{i}"][0]
+        h = 0.5 * h * (1.0 + erf(h / np.sqrt(2.0)))
+        x = ln(h @ w[f"w2_{i}"][0] + y)
+        if return_layers:
+            outs.append(x)
+    return outs if return_layers else x
