@@ -239,7 +239,11 @@ def run_reference_arm(args, cfg, workload):
     }
     extra = reference_matmul_rate()
     if extra:
-        line["reference_matmulAddF32"] = extra
+        line["cpu_baseline"]["reference_matmulAddF32"] = extra
+    try:
+        line["cpu_baseline"]["torch_cpu_fp32"] = torch_cpu_baseline(cfg, workload, budget_s=8.0)
+    except Exception as exc:
+        line["cpu_baseline"]["torch_cpu_fp32"] = {"unavailable": repr(exc)}
     print(json.dumps(line), flush=True)
 
 
@@ -402,12 +406,350 @@ def run_op_arm(args):
 
 # ------------------------------------------------------------------------- GPU arm
 
+MIN_TIMED_SECONDS = 1.0  # every throughput figure is averaged over at least this much GPU time
+
+
+class Ranks:
+    """The process group of the run (or a stand-in for one process)."""
+
+    def __init__(self, device):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.device = torch, dist, device
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def timed_region(ranks, stream, step, steps: int, min_seconds: float = MIN_TIMED_SECONDS):
+    """Times `steps` calls of `step()` per round, as many rounds back to back as it takes to fill
+    `min_seconds` (the same number on every rank), between two CUDA events on the launching
+    stream with a barrier + synchronize on both sides.  Returns (ms per step = max over ranks of
+    the whole region / steps run, steps run, seconds)."""
+    import torch
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ranks.barrier()
+    ev0.record(stream)
+    for _ in range(steps):
+        step()
+    ev1.record(stream)
+    ranks.barrier()
+    probe_ms = ranks.max(ev0.elapsed_time(ev1))
+    rounds = max(1, int(np.ceil(min_seconds * 1e3 / max(probe_ms, 1e-3))))
+    ranks.barrier()
+    ev0.record(stream)
+    for _ in range(rounds * steps):
+        step()
+    ev1.record(stream)
+    ranks.barrier()
+    total_ms = ranks.max(ev0.elapsed_time(ev1))
+    return total_ms / (rounds * steps), rounds * steps, total_ms / 1e3
+
+
+def gemm_chain(hom, cfg, weights, batch, seq, device, stream):
+    """The GEMM launches of one forward, in order and on the model's own weights, with nothing
+    in between: what the dominant kernel family costs when only it runs (neighbouring launches
+    overlap through programmatic dependent launch exactly as in the full step).  Returns a
+    callable that replays the captured chain once, the launch count and the FLOPs."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(1)
+    h = cfg.hidden
+    mk = lambda *shape: (torch.randn(shape, generator=g, device=device)).half()
+    x, res, ctx = mk(batch, seq, h), mk(batch, seq, h), mk(batch, seq, h)
+    qkv = torch.empty((batch, seq, 3 * h), dtype=torch.float16, device=device)
+    mid = torch.empty((batch, seq, cfg.ffn), dtype=torch.float16, device=device)
+
+    def issue():
+        for i in range(cfg.layers):
+            hom.cutlassGemmF16(x, weights[f"wqkv_{i}"], None, qkv)
+            hom.cutlassGemmF16(ctx, weights[f"wo_{i}"], res, x, beta=1.0)
+            hom.cutlassGemmF16(x, weights[f"w1_{i}"], None, mid, activation=1)
+            hom.cutlassGemmF16(mid, weights[f"w2_{i}"], res, x, beta=1.0)
+
+    issue()
+    hom.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        issue()
+    keep = (x, res, ctx, qkv, mid)
+    return (lambda: (graph.replay(), keep)[0]), 4 * cfg.layers, cfg.gemm_flops_per_sequence(seq) * batch
+
+
+def per_kernel_breakdown(hom, prog_factory, inputs, n_prof=5):
+    """Per-launch CUDA-event durations of one step: a second replay program is captured with the
+    library's per-launch events switched on, so every launch of its graph is bracketed by
+    event-record nodes on the launching stream.  The event nodes stand between the kernels, so
+    launches are serialised here (no overlap of a kernel's ramp with its predecessor's tail):
+    the SHARES are meaningful, the sum exceeds the step time measured without them."""
+    prog_t = prog_factory()
+    ids_d, mask_d, types_d = inputs
+    prog_t.forward(ids_d, mask_d, types_d, use_graph=True)  # first call runs eagerly (set-up)
+    hom.synchronize()
+    hom.op_timing(True)
+    prog_t.forward(ids_d, mask_d, types_d, use_graph=True)  # capture + first launch
+    hom.op_timing(False)
+    hom.synchronize()
+    records = []
+    for _ in range(n_prof):
+        prog_t.forward(ids_d, mask_d, types_d, use_graph=True)
+        hom.synchronize()
+        records += hom.peek_op_timings()
+    prog_t.close()
+    hom.collect_op_timings()  # releases the events
+    kinds = {1: "gemm", 2: "layernorm", 3: "attention", 4: "elementwise", 5: "gather", 6: "cu_seqlen"}
+    per_kind, gemm_shapes = {}, {}
+    for kind, ms, flops, nbytes in records:
+        d = per_kind.setdefault(kinds.get(kind, str(kind)), {"launches": 0, "ms": 0.0, "flops": 0.0, "bytes": 0.0})
+        d["launches"] += 1
+        d["ms"] += ms
+        d["flops"] += flops
+        d["bytes"] += nbytes
+        if kind == 1:
+            d = gemm_shapes.setdefault(f"{flops / 1e9:.2f}_gflop", {"launches": 0, "ms": 0.0, "flops": flops})
+            d["launches"] += 1
+            d["ms"] += ms
+    total_ms = sum(v["ms"] for v in per_kind.values()) or 1.0
+    kernels = {k: {"launches_per_step": v["launches"] // n_prof, "serialised_ms_per_step": v["ms"] / n_prof,
+                   "share": v["ms"] / total_ms,
+                   "tflops": (v["flops"] / (v["ms"] / 1e3) / 1e12) if v["ms"] > 0 and v["flops"] else None,
+                   "gbs": (v["bytes"] / (v["ms"] / 1e3) / 1e9) if v["ms"] > 0 else None}
+               for k, v in per_kind.items()}
+    by_shape = {k: {"launches_per_step": v["launches"] // n_prof, "serialised_avg_us": 1e3 * v["ms"] / v["launches"],
+                    "tflops": v["flops"] * v["launches"] / (v["ms"] / 1e3) / 1e12}
+                for k, v in gemm_shapes.items()}
+    gemm_bytes = per_kind.get("gemm", {}).get("bytes", 0.0) / max(1, per_kind.get("gemm", {}).get("launches", 1))
+    return kernels, by_shape, gemm_bytes
+
+
+def measure_workload(args, ranks, hom, stream, cfg, workload, name, *, full: bool):
+    """Everything that is measured for one workload on this rank's GPU; `full` adds the
+    end-to-end, eager, per-kernel, GEMM-chain and gather measurements to the device-resident
+    throughput."""
+    import torch
+    from hands_on_mlir_b200.bert_program import BertProgram, shard_batch
+    world, rank, device = ranks.world, ranks.rank, ranks.device
+    if workload["scaling"] == "weak":
+        local_batch, first = workload["batch"], rank * workload["batch"]
+        global_batch = workload["batch"] * world
+    else:
+        lo, hi = shard_batch(workload["batch"], world, rank)
+        local_batch, first, global_batch = hi - lo, lo, workload["batch"]
+    seq = workload["seq"]
+    factory = lambda: _program(BertProgram, cfg, local_batch, seq, args, weights)
+    weights = make_weights_torch(cfg, seq, device)
+    prog = factory()
+    ids_np, mask_np, types_np = make_inputs(workload, local_batch, first)
+    ids_h, mask_h, types_h = (torch.from_numpy(x).pin_memory() for x in (ids_np, mask_np, types_np))
+    ids_d, mask_d, types_d = (x.to(device) for x in (ids_h, mask_h, types_h))
+    steps = args.steps
+    out = {"local_batch": local_batch, "global_batch": global_batch, "seq": seq}
+
+    # ---- device-resident throughput (value): CUDA-graph replay, inputs already in HBM
+    for _ in range(max(args.warmup, 3)):
+        prog.forward(ids_d, mask_d, types_d, use_graph=True)
+    hom.synchronize()
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        ms, n_run, secs = timed_region(ranks, stream, lambda: prog.forward(ids_d, mask_d, types_d, use_graph=True), steps)
+    hom.synchronize()
+    out.update(ms_per_step=ms, value=global_batch / (ms / 1e3), timed_steps_total=n_run, timed_region_s=secs,
+               clocks=clocks.summary(), launches_per_forward=prog.launches_per_forward())
+    mhz = out["clocks"]["sm_mhz"]
+    out["ms_x_ghz"] = ms * mhz / 1e3 if mhz else None  # step time in millions of SM cycles: clock-independent
+    if not full:
+        kernels, _, _ = per_kernel_breakdown(hom, factory, (ids_d, mask_d, types_d), n_prof=2)
+        out["kernels"] = kernels
+        prog.close()
+        return out
+
+    # ---- the same call sequence issued eagerly (one host call per kernel, no graph): what a
+    # model library compiled by the reference does (examples/torch/bert/bert.cu:107-127)
+    for _ in range(3):
+        prog.forward(ids_d, mask_d, types_d, use_graph=False)
+    hom.synchronize()
+    ms_e, n_e, _ = timed_region(ranks, stream, lambda: prog.forward(ids_d, mask_d, types_d, use_graph=False),
+                                steps, min_seconds=0.5)
+    t0 = time.perf_counter()
+    for _ in range(20):
+        prog.forward(ids_d, mask_d, types_d, use_graph=False)
+    host_us = (time.perf_counter() - t0) / (20 * prog.launches_per_forward()) * 1e6
+    hom.synchronize()
+    out["eager"] = {"value": global_batch / (ms_e / 1e3), "unit": "sequences/s", "ms_per_step": ms_e,
+                    "steps_timed": n_e, "host_us_per_call": host_us,
+                    "note": "no CUDA graph: every runner-utils call is made from the host each step"}
+
+    # ---- end to end with host buffers (e2e): every step copies its inputs from pinned host
+    # memory and delivers its hidden states to pinned host memory; the delivery of step i
+    # overlaps the compute of step i+1 (two result slots), and the clock stops only after the
+    # last step's result is on the host.
+    outs = tuple(torch.empty((local_batch, seq, cfg.hidden), dtype=torch.float16).pin_memory() for _ in range(2))
+    for i in range(4):
+        prog.forward_host_async(ids_h, mask_h, types_h, outs[i & 1], use_graph=True)
+    prog.wait_host()
+    e2e_steps = max(steps, int(np.ceil(MIN_TIMED_SECONDS * 1e3 / ms)))
+    ranks.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        prog.forward_host_async(ids_h, mask_h, types_h, outs[i & 1], use_graph=True)
+    prog.wait_host()
+    torch.cuda.synchronize()
+    e2e_s = ranks.max(time.perf_counter() - t0)
+    ranks.barrier()
+    h2d, d2h = prog.host_traffic()
+    out["e2e"] = {"value": global_batch * e2e_steps / e2e_s, "unit": "sequences/s", "h2d_bytes_per_step": h2d,
+                  "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / e2e_steps, "steps_timed": e2e_steps}
+
+    # ---- the GEMM family alone (roofline) and the per-kernel shares
+    replay_chain, n_gemm, chain_flops = gemm_chain(hom, cfg, weights, local_batch, seq, device, stream)
+    for _ in range(3):
+        replay_chain()
+    with ClockSampler(torch.cuda.current_device()) as chain_clocks:
+        ms_chain, _, _ = timed_region(ranks, stream, replay_chain, max(10, steps // 4))
+    kernels, by_shape, gemm_bytes = per_kernel_breakdown(hom, factory, (ids_d, mask_d, types_d))
+    out.update(kernels=kernels, gemm_by_shape=by_shape)
+    peaks, peak_src = load_peaks()
+    achieved = chain_flops / (ms_chain / 1e3) / 1e12
+    cc = chain_clocks.summary()
+    capped = bool(cc["sm_mhz"] and cc["sm_max_mhz"] and cc["sm_mhz"] < 0.95 * cc["sm_max_mhz"])
+    peak = peaks["bf16_tflops_sustained"] if capped else peaks["bf16_tflops"]
+    out["roofline"] = {
+        "bound": "tensor", "kernel": "gemm_f16_pair_kernel / gemm_f16_kernel (all GEMM launches of a step)",
+        "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+        "peak_source": f"{peak_src}: " + ("sustained dense bf16/fp16 (SM clock below 95 % of max while timed)"
+                                         if capped else "burst dense bf16/fp16 (SM clock at max while timed)"),
+        "frac_of_burst": achieved / peaks["bf16_tflops"],
+        "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+        "how": f"the step's {n_gemm} GEMM launches replayed as one CUDA graph with nothing in between, "
+               f">= {MIN_TIMED_SECONDS:.0f} s between two CUDA events on the launching stream; "
+               "achieved = algorithmic FLOPs / that time",
+        "gemm_ms_per_step": ms_chain, "launches_per_step": n_gemm, "avg_launch_us": 1e3 * ms_chain / n_gemm,
+        "clocks": cc, "traffic": ncu_traffic(name)[0], "traffic_source": ncu_traffic(name)[1],
+        "algorithmic_bytes_per_launch": gemm_bytes,
+    }
+
+    # ---- final gather of the hidden states (the only collective): warm, on a side stream, the
+    # gather of step i overlapping the compute of step i+1
+    if world > 1:
+        dist = ranks.dist
+        side = torch.cuda.Stream()
+        res0 = prog.result_to_torch(prog.forward(ids_d, mask_d, types_d, use_graph=True))
+        slots = [torch.empty_like(res0) for _ in range(2)]
+        gathered = [torch.empty((world,) + tuple(res0.shape), dtype=res0.dtype, device=device) for _ in range(2)]
+        done = [torch.cuda.Event() for _ in range(2)]
+
+        def step_with_gather(i):
+            mem = prog.forward(ids_d, mask_d, types_d, use_graph=True)
+            slot = slots[i & 1]
+            if i >= 2:
+                stream.wait_event(done[i & 1])  # the gather that last read this slot has finished
+            # the program's result buffer is overwritten by the next forward: park the result
+            slot.copy_(_device_view(torch, mem, res0), non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                dist.all_gather_into_tensor(gathered[i & 1], slot)
+                done[i & 1].record(side)
+
+        for i in range(4):
+            step_with_gather(i)
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(side):
+            g0.record(side)
+            dist.all_gather_into_tensor(gathered[0], slots[0])
+            g1.record(side)
+        torch.cuda.synchronize()
+        out["output_gather_ms"] = ranks.max(g0.elapsed_time(g1))
+        n_g = max(steps, int(np.ceil(MIN_TIMED_SECONDS * 1e3 / ms)))
+        ranks.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n_g):
+            step_with_gather(i)
+        stream.wait_stream(side)
+        e1.record(stream)
+        ranks.barrier()
+        ms_g = ranks.max(e0.elapsed_time(e1)) / n_g
+        out["value_with_gather"] = global_batch / (ms_g / 1e3)
+        out["with_gather"] = {"ms_per_step": ms_g, "steps_timed": n_g,
+                              "bytes_gathered_per_rank_per_step": int(res0.numel() * 2 * world),
+                              "how": "NCCL all-gather of every step's hidden states on a side stream, "
+                                     "overlapping the next step's compute; the clock stops after the last gather"}
+    prog.close()
+    return out
+
+
+def _device_view(torch, memref, like):
+    """A torch view (no copy) of the program-owned fp16 result buffer."""
+    return torch.as_tensor(_CudaArray(memref.data_ptr, tuple(like.shape)), device=like.device)
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ wrapper around a device pointer holding fp16 values."""
+
+    def __init__(self, ptr: int, shape):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<f2", "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+
+
+def _program(BertProgram, cfg, batch, seq, args, weights):
+    prog = BertProgram(cfg, batch, seq, fused_embedding=args.fused_embedding,
+                       fused_layernorm=args.fused_layernorm)
+    prog.set_weights(weights)
+    return prog
+
+
+def torch_cpu_baseline(cfg, workload, budget_s: float = 10.0):
+    """PyTorch CPU fp32 encoder (all host cores) on a bounded sample: the same math as the
+    oracle without the fp16 rounding points, as an optimised-CPU-library figure beside the
+    scalar port."""
+    import torch
+    seq, h, heads = workload["seq"], cfg.hidden, cfg.heads
+    g = torch.Generator().manual_seed(0)
+    w = {n: torch.randn(cfg.weight_shape(n, seq), generator=g) * 0.02 for n in cfg.weight_names()}
+
+    def run(n_seq):
+        ids, mask, types = (torch.from_numpy(x) for x in make_inputs(workload, n_seq, 0))
+        ln = lambda z: torch.nn.functional.layer_norm(z, (h,), eps=cfg.eps)
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            x = ln(w["word_emb"][0][ids] + w["type_emb"][0][types] + w["pos_emb"][0][None, :seq])
+            add_mask = (1.0 - mask.float())[:, None, None, :] * torch.finfo(torch.float32).min
+            for i in range(cfg.layers):
+                qkv = (x @ w[f"wqkv_{i}"][0]).view(n_seq, seq, 3, heads, h // heads)
+                q, k, v = (qkv[:, :, j].permute(0, 2, 1, 3) for j in range(3))
+                a = torch.softmax(q @ k.transpose(-1, -2) / (h // heads) ** 0.5 + add_mask, -1) @ v
+                a = a.permute(0, 2, 1, 3).reshape(n_seq, seq, h)
+                x = ln(a @ w[f"wo_{i}"][0] + x)
+                x = ln(torch.nn.functional.gelu(x @ w[f"w1_{i}"][0]) @ w[f"w2_{i}"][0] + x)
+        return time.perf_counter() - t0
+
+    run(1)
+    one = run(1)
+    n_seq = int(max(1, min(workload["batch"], budget_s // max(one, 1e-3))))
+    secs = run(n_seq)
+    return {"value": n_seq / secs, "unit": "sequences/s", "cores": torch.get_num_threads(), "kind": "torch-cpu-fp32",
+            "sample": f"{n_seq} of {workload['batch']} sequences x {seq} tokens, all {cfg.layers} layers, {secs:.1f} s"}
+
+
 def run_gpu_arm(args, cfg, workload):
     import torch
     import torch.distributed as dist
     from __graft_entry__ import load_package
 
-    rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
@@ -434,154 +776,35 @@ def run_gpu_arm(args, cfg, workload):
             os.close(saved_stdout)
 
     pkg = load_package()
-    from hands_on_mlir_b200.bert_program import BertProgram, shard_batch
+    from hands_on_mlir_b200.bert_program import BertConfig
     hom = pkg.runner()
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     hom.use_torch_stream()
+    ranks = Ranks(device)
+    rank = ranks.rank
 
-    if workload["scaling"] == "weak":
-        local_batch, first = workload["batch"], rank * workload["batch"]
-        global_batch = workload["batch"] * world
-    else:
-        lo, hi = shard_batch(workload["batch"], world, rank)
-        local_batch, first, global_batch = hi - lo, lo, workload["batch"]
-    seq = workload["seq"]
+    m = measure_workload(args, ranks, hom, stream, cfg, workload, args.workload, full=True)
 
-    prog = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding,
-                       fused_layernorm=args.fused_layernorm)
-    weights = make_weights_torch(cfg, seq, device)
-    prog.set_weights(weights)
-    ids_np, mask_np, types_np = make_inputs(workload, local_batch, first)
-    ids_h, mask_h, types_h = (torch.from_numpy(x).pin_memory() for x in (ids_np, mask_np, types_np))
-    out_h = torch.empty((local_batch, seq, cfg.hidden), dtype=torch.float16).pin_memory()
-    ids_d, mask_d, types_d = (x.to(device) for x in (ids_h, mask_h, types_h))
+    # ---- the split configuration (BERT-large 256 x 512 divided over the GPUs) beside the headline
+    config5 = None
+    if args.workload == "bert-base" and not args.no_config5:
+        wl5 = WORKLOADS["bert-large"]
+        saved = args.steps
+        args.steps = max(10, min(saved, 20))
+        r5 = measure_workload(args, ranks, hom, stream, BertConfig.large(), wl5, "bert-large", full=False)
+        args.steps = saved
+        cfg5 = BertConfig.large()
+        fl5 = cfg5.gemm_flops_per_sequence(wl5["seq"]) + cfg5.attention_flops_per_sequence(wl5["seq"])
+        config5 = {"workload": f"bert-large encoder (24 layers, hidden 1024), global batch {r5['global_batch']} x seq "
+                               f"{wl5['seq']} split evenly: {r5['local_batch']} sequences per GPU, valid lengths U[256, 512]",
+                   "metric": "bert_fp16_sequences_per_s", "value": r5["value"], "unit": "sequences/s",
+                   "n_gpus": world, "scaling": "strong", "ms_per_step": r5["ms_per_step"],
+                   "steps_timed": r5["timed_steps_total"], "timed_region_s": r5["timed_region_s"],
+                   "model_tflops": r5["value"] * fl5 / 1e12, "clocks": r5["clocks"],
+                   "kernel_shares": {k: round(v["share"], 4) for k, v in r5["kernels"].items()}}
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- device-resident throughput (value)
-    for _ in range(max(args.warmup, 3)):
-        prog.forward(ids_d, mask_d, types_d, use_graph=True)
-    hom.synchronize()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        ev0.record(stream)
-        for _ in range(args.steps):
-            prog.forward(ids_d, mask_d, types_d, use_graph=True)
-        ev1.record(stream)
-        barrier()
-    hom.synchronize()
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
-    value = global_batch * args.steps / (ms_total / 1e3)
-
-    # ---- end to end with host buffers (e2e): every step copies its inputs from pinned host
-    # memory and delivers its hidden states to pinned host memory; the delivery of step i
-    # overlaps the compute of step i+1 (two result slots), and the clock stops only after the
-    # last step's result is on the host.
-    out_h2 = torch.empty_like(out_h).pin_memory()
-    outs = (out_h, out_h2)
-    for i in range(4):
-        prog.forward_host_async(ids_h, mask_h, types_h, outs[i & 1], use_graph=True)
-    prog.wait_host()
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        prog.forward_host_async(ids_h, mask_h, types_h, outs[i & 1], use_graph=True)
-    prog.wait_host()
-    torch.cuda.synchronize()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
-    barrier()
-    h2d, d2h = prog.host_traffic()
-    e2e_value = global_batch * args.steps / e2e_s
-
-    # ---- per-launch durations of a step (roofline): a second replay program is captured with
-    # the library's per-launch CUDA events switched on, so every launch of its graph is bracketed
-    # by event-record nodes on the launching stream; the graph is replayed and read out n_prof
-    # times.  (The event nodes stand between the kernels, so this pass runs without the
-    # programmatic overlap of neighbouring launches that the timed region above has.)
-    prog_t = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding,
-                         fused_layernorm=args.fused_layernorm)
-    prog_t.set_weights(weights)
-    prog_t.forward(ids_d, mask_d, types_d, use_graph=True)  # first call runs eagerly (set-up)
-    hom.synchronize()
-    hom.op_timing(True)
-    prog_t.forward(ids_d, mask_d, types_d, use_graph=True)  # capture + first launch
-    hom.op_timing(False)
-    hom.synchronize()
-    n_prof = 5
-    records = []
-    for _ in range(n_prof):
-        prog_t.forward(ids_d, mask_d, types_d, use_graph=True)
-        hom.synchronize()
-        records += hom.peek_op_timings()
-    prog_t.close()
-    hom.collect_op_timings()  # releases the events
-    kinds = {1: "gemm", 2: "layernorm", 3: "attention", 4: "elementwise", 5: "gather", 6: "cu_seqlen"}
-    per_kind = {}
-    for kind, ms, flops, nbytes in records:
-        d = per_kind.setdefault(kinds.get(kind, str(kind)), {"launches": 0, "ms": 0.0, "flops": 0.0,
-                                                              "bytes": 0.0})
-        d["launches"] += 1
-        d["ms"] += ms
-        d["flops"] += flops
-        d["bytes"] += nbytes
-    # GEMM launches grouped by their algorithmic FLOPs (= by shape)
-    gemm_shapes = {}
-    for kind, ms, flops, nbytes in records:
-        if kind == 1:
-            d = gemm_shapes.setdefault(f"{flops / 1e9:.2f}_gflop", {"launches": 0, "ms": 0.0, "flops": flops})
-            d["launches"] += 1
-            d["ms"] += ms
-    gemm_by_shape = {k: {"launches_per_step": v["launches"] // n_prof,
-                         "avg_us": 1e3 * v["ms"] / v["launches"],
-                         "tflops": v["flops"] * v["launches"] / (v["ms"] / 1e3) / 1e12}
-                     for k, v in gemm_shapes.items()}
-    peaks, peak_src = load_peaks()
-    gemm = per_kind.get("gemm", {"launches": 1, "ms": float("nan"), "flops": 0.0})
-    gemm_tflops = gemm["flops"] / (gemm["ms"] / 1e3) / 1e12 if gemm["ms"] > 0 else float("nan")
-    tensor_peak = peaks["bf16_tflops_sustained"]
-    roofline = {
-        "bound": "tensor", "kernel": "gemm_f16_kernel (all GEMM launches of a step)",
-        "achieved": gemm_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
-        "frac": gemm_tflops / tensor_peak, "peak_source": f"{peak_src} (sustained dense bf16/fp16)",
-        "traffic": ncu_traffic(args.workload)[0],
-        "traffic_source": ncu_traffic(args.workload)[1],
-        "algorithmic_bytes_per_launch": gemm["bytes"] / max(1, gemm["launches"]),
-        "launches_per_step": gemm["launches"] // n_prof,
-        "avg_launch_us": 1e3 * gemm["ms"] / max(1, gemm["launches"]),
-    }
-    kernel_share = {k: {"launches_per_step": v["launches"] // n_prof,
-                        "ms_per_step": v["ms"] / n_prof,
-                        "tflops": (v["flops"] / (v["ms"] / 1e3) / 1e12) if v["ms"] > 0 and v["flops"] else None,
-                        "gbs": (v["bytes"] / (v["ms"] / 1e3) / 1e9) if v["ms"] > 0 else None}
-                    for k, v in per_kind.items()}
-
-    # ---- final gather of the hidden states (the only collective; not on the data path)
-    gather_ms = None
-    if world > 1:
-        res = prog.result_to_torch(prog.forward(ids_d, mask_d, types_d, use_graph=True))
-        bufs = [torch.empty_like(res) for _ in range(world)]
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        dist.all_gather(bufs, res)
-        g1.record(stream)
-        torch.cuda.synchronize()
-        gather_ms = max_over_ranks(g0.elapsed_time(g1))
-
-    # ---- CPU baseline on a bounded sample (rank 0, N = 1 only)
+    # ---- CPU baselines on bounded samples (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         enc = CpuEncoder(cfg, workload)
@@ -590,40 +813,57 @@ def run_gpu_arm(args, cfg, workload):
         cpu = {"value": n_seq * (layers / cfg.layers) / secs, "unit": "sequences/s",
                "cores": enc.threads, "kind": "port",
                "sample": enc.describe(n_seq, layers) + f", {secs:.1f} s"}
+        try:
+            cpu["torch_cpu_fp32"] = torch_cpu_baseline(cfg, workload)
+        except Exception as exc:  # a baseline, never a reason to lose the GPU line
+            cpu["torch_cpu_fp32"] = {"unavailable": repr(exc)}
+        ref = reference_matmul_rate()
+        if ref:
+            cpu["reference_matmulAddF32"] = ref
 
     if rank == 0:
+        seq = workload["seq"]
         flops_per_seq = cfg.gemm_flops_per_sequence(seq) + cfg.attention_flops_per_sequence(seq)
         line = {
-            "metric": "bert_fp16_sequences_per_s", "value": value, "unit": "sequences/s",
+            "metric": "bert_fp16_sequences_per_s", "value": m["value"], "unit": "sequences/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "ms_per_step": m["ms_per_step"], "higher_is_better": True,
             "scaling": workload["scaling"], "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
             "config": {
                 "workload": f"{args.workload} encoder ({cfg.layers} layers, hidden {cfg.hidden}, "
-                            f"{cfg.heads} heads, FFN {cfg.ffn}), global batch {global_batch} x seq "
-                            f"{seq}, {local_batch} sequences per GPU",
+                            f"{cfg.heads} heads, FFN {cfg.ffn}), global batch {m['global_batch']} x seq "
+                            f"{seq}, {m['local_batch']} sequences per GPU",
                 "parallelism": f"batch-sharded replicas x{world}, no data-path collective",
                 "l2": "no explicit flush: the per-step working set (all layer weights + "
                       "activations) exceeds the 126 MB L2",
                 "launch": "CUDA-graph replay of the runner-utils call sequence"
                           + (" with the fused embedding extension" if args.fused_embedding else "")
                           + (" with the fused GEMM+LayerNorm extension" if args.fused_layernorm else ""),
+                "timing": f"{args.steps}-step rounds repeated back to back for >= {MIN_TIMED_SECONDS:.0f} s "
+                          "between one pair of CUDA events; ms_per_step is the mean over all of them",
             },
-            "model_tflops": value * flops_per_seq / 1e12,
-            "e2e": {"value": e2e_value, "unit": "sequences/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps},
-            "gpu_launches": args.steps * prog.launches_per_forward(),
-            "roofline": roofline,
-            "kernels": kernel_share,
-            "gemm_by_shape": gemm_by_shape,
-            "clocks": clocks.summary(),
-            "output_gather_ms": gather_ms,
+            "timed_steps_total": m["timed_steps_total"], "timed_region_s": m["timed_region_s"],
+            "ms_per_step_x_sm_ghz": m["ms_x_ghz"],
+            "model_tflops": m["value"] * flops_per_seq / 1e12,
+            "e2e": m["e2e"],
+            "eager": m["eager"],
+            "gpu_launches": m["timed_steps_total"] * m["launches_per_forward"],
+            "gpu_launches_per_step": m["launches_per_forward"],
+            "roofline": m["roofline"],
+            "kernels": m["kernels"],
+            "gemm_by_shape": m["gemm_by_shape"],
+            "clocks": m["clocks"],
+            "output_gather_ms": m.get("output_gather_ms"),
         }
+        if "value_with_gather" in m:
+            line["value_with_gather"] = m["value_with_gather"]
+            line["with_gather"] = m["with_gather"]
+        if config5:
+            line["config5"] = config5
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
-    prog.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -636,6 +876,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bert-base")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-config5", action="store_true",
+                    help="skip the bert-large (batch 256 x seq 512, split over the GPUs) sub-record")
     ap.add_argument("--fused-layernorm", action="store_true",
                     help="replace the GEMM + LayerNorm call pairs (out-projection, FFN2) by "
                          "homGemmResidualLayernormF16 (an extension; off by default like "

@@ -94,7 +94,15 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  HOM_DIAG(if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);)
+  HOM_DIAG(unsigned long long g_entry = 0; if (p.tl) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
+           if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);)
+  // The first TMA instruction stalls until its descriptor has been fetched: start those
+  // fetches before anything else so that they overlap the barrier and tensor-memory set-up.
+  if (threadIdx.x == 64) {
+    prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmD);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -117,6 +125,12 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   // Dependents may be scheduled only now that this grid's CTAs hold their tensor memory.
   pdl_launch_dependents();
+  // longest set-up (entry -> barriers, tensor memory and cluster barrier done) over the CTAs, ns
+  HOM_DIAG(if (p.tl && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    atomicMax(p.tl + 480, static_cast<long long>(t - g_entry));
+  })
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -124,10 +138,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // arms the barriers and issues the copies.
     {
       const bool leader = elect_one();
-      if (leader) {
-        prefetch_tensormap(&tmA);
-        prefetch_tensormap(&tmB);
-      }
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -166,6 +176,12 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           load_b(i, kb0 + i, nb0);
         }
       }
+      // longest entry -> first weight tiles requested (just before the dependency wait), ns
+      HOM_DIAG(if (p.tl && leader) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMax(p.tl + 481, static_cast<long long>(t - g_entry));
+      })
       pdl_wait();
       HOM_DIAG(if (p.tl && leader) timeline_stamp(p.tl, 2);)
       for (int unit = pair; unit < p.num_units && ok; unit += num_pairs) {

@@ -111,6 +111,13 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   HOM_DIAG(const long long t_entry = p.prof ? clock64() : 0; unsigned long long g_entry = 0;
            if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
            if (p.tl && threadIdx.x == 0) timeline_stamp(p.tl, 0);)
+  // The first TMA instruction stalls until its descriptor has been fetched: start those
+  // fetches before anything else so that they overlap the barrier and tensor-memory set-up.
+  if (threadIdx.x == 64) {
+    prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmD);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -143,10 +150,6 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // arms the barriers and issues the copies.
     {
       const bool leader = elect_one();
-      if (leader) {
-        prefetch_tensormap(&tmA);
-        prefetch_tensormap(&tmB);
-      }
       int s = 0;
       uint32_t ph = 0, armed = 0;
       bool ok = true;

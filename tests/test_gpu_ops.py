@@ -130,6 +130,33 @@ def test_gemm_small_batch_ffn2_default_choice_uses_a_split(hom, cuda, oracle):
     assert_close_f16(got, oracle.gemm_f16(A, B, C, beta=1.0), "FFN2 batch 1, default choice")
 
 
+@pytest.mark.parametrize("tile", [3, 6])
+def test_gemm_b_operand_produced_by_the_previous_call_on_the_stream(hom, cuda, oracle, tile):
+    """B is written by the elementwise kernel launched just before the GEMM on the same stream,
+    with no synchronisation in between.  Kernels overlap their neighbours' tails (programmatic
+    dependent launch); only a B that was DECLARED constant (homDeclareWeights, allocConstant*)
+    may be fetched before the previous kernel has finished, so this B must be read after it was
+    written.  Repeated so that a stale read would not hide behind lucky timing."""
+    import torch
+    rng = _rng(60)
+    m, k, n = 2048, 768, 768
+    A = rng.uniform(-1, 1, (1, m, k)).astype(np.float16)
+    B1 = rng.normal(0, 0.03, (1, k, n)).astype(np.float16)
+    tA, tB1 = to_dev(A, cuda), to_dev(B1, cuda)
+    tB = torch.empty_like(tB1)
+    tD = torch.empty((1, m, n), dtype=torch.float16, device=cuda)
+    for rep in range(4):
+        B2 = rng.normal(0, 0.03, (1, k, n)).astype(np.float16)
+        tB2 = to_dev(B2, cuda)
+        tB.zero_()
+        hom.synchronize()
+        hom.thrustElementwiseAddF16(tB1, tB2, tB)
+        hom.cutlassGemmF16(tA, tB, None, tD, gemmNum=tile)
+        hom.synchronize()
+        want = oracle.gemm_f16(A, oracle.elementwise("Add", B1, B2))
+        assert_close_f16(tD.cpu().numpy(), want, f"B produced on the stream, repeat {rep}")
+
+
 def test_gemm_alpha_beta_gelu(hom, cuda, oracle):
     rng = _rng(8)
     A = rng.normal(0, 1, (1, 256, 192)).astype(np.float16)
