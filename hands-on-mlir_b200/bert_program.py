@@ -220,6 +220,7 @@ class ModelLibrary:
         lib.homModelLastError.restype = ctypes.c_char_p
         lib.homModelLastError.argtypes = [c_void_p]
         lib.homModelClose.argtypes = [c_void_p]
+        lib.homModelSetSynchronous.argtypes = [c_void_p, c_int]
         self._lib = lib
         self._handle = lib.homModelOpen(str(so_path).encode())
         if not self._handle:
@@ -244,6 +245,10 @@ class ModelLibrary:
             runner().check()
             raise HomError(rc, (self._lib.homModelLastError(self._handle) or b"").decode())
         return res
+
+    def set_synchronous(self, enable: bool = True):
+        """Make invoke() wait for the stream and surface device-side errors (homSynchronize)."""
+        self._lib.homModelSetSynchronous(self._handle, int(enable))
 
     def init_tensor_count(self, fn: str) -> int:
         return int(self._lib.homModelInitTensorCount(self._handle, fn.encode()))

@@ -92,7 +92,9 @@ def build(force: bool = False, verbose: bool = False, diagnostics: bool = False)
     lib_dir = LIB_DIR / "diagnostics" if diagnostics else LIB_DIR
     obj_dir = OBJ_DIR / "diagnostics" if diagnostics else OBJ_DIR
     runner_lib, replay_lib = lib_dir / RUNNER_LIB.name, lib_dir / REPLAY_LIB.name
-    extra = ("-DHOM_DIAGNOSTICS",) if diagnostics else ()
+    # The diagnostics build also brackets every launch in an NVTX range named after its op family
+    # (hom.gemm, hom.attention, ...), for timelines taken with an external profiler.
+    extra = ("-DHOM_DIAGNOSTICS", "-DHOM_NVTX") if diagnostics else ()
     lib_dir.mkdir(parents=True, exist_ok=True)
     obj_dir.mkdir(parents=True, exist_ok=True)
     hdr_mtime = _newest_header_mtime()

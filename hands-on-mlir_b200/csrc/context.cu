@@ -11,6 +11,10 @@
 
 #include "hom_common.cuh"
 
+#ifdef HOM_NVTX
+#include <nvtx3/nvToolsExt.h>
+#endif
+
 namespace hom {
 
 namespace {
@@ -195,8 +199,27 @@ void record_event(cudaEvent_t ev, cudaStream_t stream) {
 }
 }  // namespace
 
+#ifdef HOM_NVTX
+namespace {
+const char *op_kind_name(OpKind kind) {
+  switch (kind) {
+    case kOpGemm: return "hom.gemm";
+    case kOpLayernorm: return "hom.layernorm";
+    case kOpAttention: return "hom.attention";
+    case kOpElementwise: return "hom.elementwise";
+    case kOpGather: return "hom.gather";
+    case kOpCuSeqLen: return "hom.cu_seqlen";
+  }
+  return "hom.op";
+}
+}  // namespace
+#endif
+
 LaunchScope::LaunchScope(OpKind kind, double flops, double bytes, bool may_allocate) {
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
+#ifdef HOM_NVTX
+  nvtxRangePushA(op_kind_name(kind));  // one range per entry-point launch (compile-time switch)
+#endif
   if (!may_allocate || !g_timing_enabled.load(std::memory_order_relaxed)) return;
   TimingRecord rec{kind, flops, bytes, nullptr, nullptr};
   if (cudaEventCreate(&rec.start) != cudaSuccess) return;
@@ -211,6 +234,9 @@ LaunchScope::LaunchScope(OpKind kind, double flops, double bytes, bool may_alloc
 }
 
 LaunchScope::~LaunchScope() {
+#ifdef HOM_NVTX
+  nvtxRangePop();
+#endif
   if (slot_ < 0) return;
   std::lock_guard<std::mutex> lock(g_timing_mutex);
   if (slot_ < static_cast<int>(g_timing_log.size()))

@@ -7,15 +7,17 @@
 // shared memory for the same MMA time, which is what the TMA ring needs to keep the tensor
 // pipe fed; the freed shared memory holds five stages and the epilogue staging.
 //
-//   warp 0      TMA producer (one thread)
+//   warp 0      TMA producer
 //   warp 1      tensor-memory allocation (both CTAs) and MMA issue (even CTA only)
-//   warps 2-9   epilogue: two warps per tensor-memory lane quarter, each draining half of the
-//               tile's columns: tcgen05.ld, fp32 alpha/beta/bias/erf-GELU, fp16 results staged
-//               in swizzled shared memory and written out by TMA stores
+//   warps 2-17  epilogue: four warps per tensor-memory lane quarter, each draining one
+//               64-column group of the tile: tcgen05.ld, fp32 alpha/beta/bias/erf-GELU, fp16
+//               results staged in swizzled shared memory and written out by TMA stores
 //
 // Hand-offs: full[s] lives in the even CTA (armed by its producer for the bytes of both CTAs);
 // empty[s] and acc_full[a] exist in both CTAs and are signalled by tcgen05.commit addressed to
-// both; acc_empty[a] lives in the even CTA (16 arrivals: 8 epilogue warps x 2 CTAs).
+// both; acc_empty[a] lives in the even CTA (32 arrivals: 16 epilogue warps x 2 CTAs).
+// A work unit is a 256 x BN2 tile or one of the `split_k` K ranges of a tile (SplitK,
+// gemm_epilogue.cuh).
 #include <cstdio>
 #include <cstdlib>
 

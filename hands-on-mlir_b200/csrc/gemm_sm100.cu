@@ -1,16 +1,18 @@
 // fp16 GEMM family for sm_100a: D = epilogue(alpha * A.B + beta * C), fp32 accumulate in
 // tensor memory, Row,Row,Row operands (B as [K,N]) or the "transb" form (B as [N,K]).
 //
-// One persistent CTA per SM walks a static list of 128 x BN output tiles.  Inside a CTA:
-//   warp 0    TMA producer: 128x64 A box + BN x 64 B boxes per K block into a ring of
-//             128-byte-swizzled shared-memory stages (mbarrier full/empty hand-off);
-//   warp 1    one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
-//             accumulators and releases stages / publishes accumulators with tcgen05.commit;
-//   warps 2-9 epilogue (two warps per tensor-memory lane quarter, each a share of the tile's
-//             columns): tcgen05.ld the finished accumulator (one output row per thread, 64
-//             columns at a time), fp32 alpha/beta/bias/erf-GELU, one fp16 rounding, results
-//             staged in swizzled shared memory and written out by TMA stores, while warp 1
-//             already fills the other accumulator.
+// One persistent CTA per SM walks a static list of work units: a 128 x BN output tile, or one
+// of the `split_k` K ranges of a tile.  Inside a CTA (576 threads):
+//   warp 0      TMA producer: 128x64 A box + BN x 64 B boxes per K block into a ring of
+//               128-byte-swizzled shared-memory stages (mbarrier full/empty hand-off);
+//   warp 1      issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators and
+//               releases stages / publishes accumulators with tcgen05.commit;
+//   warps 2-17  epilogue (four warps per tensor-memory lane quarter, one 64-column group of
+//               the tile each): tcgen05.ld the finished accumulator (one output row per
+//               thread, 32 columns at a time), fp32 alpha/beta/bias/erf-GELU, one fp16
+//               rounding, results staged in swizzled shared memory and written out by TMA
+//               stores, while warp 1 already fills the other accumulator.  The units of a split
+//               tile are reduced serially through an fp32 workspace (SplitK, gemm_epilogue.cuh).
 //
 // This replaces the reference's CUTLASS 2.x mma.sync kernels and its compile-time autotuner
 // (include/NVGPUKernels/GemmRunner.h:119-310, lib/NVGPUKernels/GemmProfiler.cu:143-236) with a

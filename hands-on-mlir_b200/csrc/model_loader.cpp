@@ -33,6 +33,7 @@ struct Model {
   void *handle = nullptr;
   std::map<std::string, InitTensors> init;
   std::string error;
+  bool synchronous = false;  // homModelInvoke waits for the stream and reports device-side errors
 };
 
 using InvokeFn = void (*)(void **);
@@ -106,7 +107,15 @@ int homModelInvoke(void *model, const char *fn, int32_t n_user_slots, void **use
   for (int32_t i = 0; i < n_user_slots; ++i) args.push_back(user_slots[i]);
   args.push_back(result_storage);
   forward(args.data());
+  // A device-side wait that expired only shows once the stream has drained: callers that
+  // asked for it get the stream synchronised and the status word folded in before returning.
+  if (m->synchronous) return homSynchronize();
   return homGetLastError();
+}
+
+void homModelSetSynchronous(void *model, int enable) {
+  auto *m = static_cast<Model *>(model);
+  if (m) m->synchronous = enable != 0;
 }
 
 void homModelClose(void *model) {

@@ -106,6 +106,11 @@ HOM_EXPORT int32_t homBertLaunchesPerForward(void *program);
 HOM_EXPORT void *homModelOpen(const char *so_path);
 HOM_EXPORT int homModelInvoke(void *model, const char *fn, int32_t n_user_slots, void **user_slots,
                               void *result_storage);
+/* With enable != 0, homModelInvoke waits for the library's stream after the model function
+ * returns and reports what homSynchronize() reports, so that a device-side wait that expired
+ * (error 4) reaches the loader's caller; the default (0) returns as soon as the calls are
+ * enqueued, like the reference's loader. */
+HOM_EXPORT void homModelSetSynchronous(void *model, int enable);
 HOM_EXPORT int32_t homModelInitTensorCount(void *model, const char *fn);
 HOM_EXPORT const char *homModelLastError(void *model);
 HOM_EXPORT void homModelClose(void *model);

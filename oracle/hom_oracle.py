@@ -26,7 +26,10 @@ _lib = None
 
 def build() -> None:
     """(Re)build libhom_oracle.so and, when the reference checkout is present, _ref/."""
-    subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    import os
+    cand = os.environ.get("HOM_REFERENCE_DIR") or str(HERE.parent.parent / "reference")
+    extra = [f"REFERENCE_DIR={cand}"] if (Path(cand) / "lib" / "ExecutionEngine").is_dir() else []
+    subprocess.run(["make", "-C", str(HERE)] + extra, check=True, capture_output=True)
 
 
 def lib():

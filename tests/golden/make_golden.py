@@ -1,8 +1,8 @@
 """Generates the committed golden fixtures under tests/golden/.
 
-Run in a container that has the reference checkout (default /root/reference) and PyTorch:
+Run where a checkout of the reference and PyTorch are available:
 
-    python tests/golden/make_golden.py [REFERENCE_DIR]
+    python tests/golden/make_golden.py REFERENCE_DIR
 
 * verify_gemm_ln_gemm.npz — produced by EXECUTING the reference's own
   examples/torch/layernorm/cuda/verify.py (its literal A[4x32], B[32x8], C[8x16] and the
@@ -73,7 +73,9 @@ def torch_ops():
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py REFERENCE_DIR (the reference checkout to execute verify.py from)")
+    ref = Path(sys.argv[1])
     from_reference_verify(ref)
     torch_ops()
     for f in sorted(HERE.glob("*.npz")):

@@ -409,6 +409,8 @@ def test_loader_runs_a_model_library_against_the_runner(hom, cuda, oracle, tmp_p
     tx = to_dev(X, cuda)
     for _ in range(2):
         res = model.invoke("forward", [MemRef.of(tx)])
+    model.set_synchronous(True)  # invoke now waits for the stream and would raise on a device-side error
+    res = model.invoke("forward", [MemRef.of(tx)])
     assert model.init_tensor_count("forward") == 2
     out = MemRef.from_unranked(res)
     assert out.shape == [2, 128, 96]
