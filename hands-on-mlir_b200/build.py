@@ -39,6 +39,7 @@ RUNNER_SOURCES = [
     "gemm_sm100.cu",
     "gemm_pair_sm100.cu",
     "attention_sm100.cu",
+    "attention_pingpong_sm100.cu",
     "bandwidth_kernels.cu",
     "runner_utils.cu",
     "no_alloc_entry.cu",

@@ -695,6 +695,9 @@ bool make_out_map(const void *ptr, uint64_t hidden, uint64_t seq, uint64_t bs, C
 
 bool run(const Problem &pb, cudaStream_t stream) {
   if (pb.bs == 0 || pb.seq == 0 || pb.heads == 0) return true;
+  // More than one KV tile: the two-query-tile kernel (it folds the positive softmax scale into
+  // the row maximum; any other scale takes the general kernel below).
+  if (pb.seq > kTile && pb.scale > 0.f HOM_DIAG(&& !std::getenv("HOM_ATTN_SERIAL"))) return run_pingpong(pb, stream);
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

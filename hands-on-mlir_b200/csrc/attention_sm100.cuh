@@ -15,6 +15,8 @@ struct Problem {
 };
 
 bool run(const Problem &pb, cudaStream_t stream);
+// seq > 128: the persistent kernel that owns two query tiles per CTA (attention_pingpong_sm100.cu).
+bool run_pingpong(const Problem &pb, cudaStream_t stream);
 
 }  // namespace attention
 }  // namespace hom

@@ -335,6 +335,28 @@ def test_attention_seq_not_multiple_of_tile(hom, cuda, oracle):
     _attention_case(hom, cuda, oracle, 3, 192, 2, np.array([192, 100, 129]), 7)
 
 
+@pytest.mark.parametrize("seq,lens", [
+    (192, [192, 1, 128, 129, 191, 0]),        # one full + one ragged query tile
+    (320, [320, 257, 256, 130, 64, 300]),     # two query-tile pairs, the second half empty
+    (448, [448, 385, 384, 383, 129, 2]),      # four query tiles, every raggedness
+    (512, [512, 511, 384, 257, 256, 128]),
+    (1024, [1024, 700, 513, 100]),            # eight KV tiles: the K / V ring wraps many times
+])
+def test_attention_two_query_tiles_per_cta(hom, cuda, oracle, seq, lens):
+    """Sequences longer than one tile go to the kernel that owns two query tiles per CTA and
+    walks (batch, head, tile pair) work items: more items than CTAs are not needed for
+    coverage here, ragged lengths and empty tiles are."""
+    _attention_case(hom, cuda, oracle, len(lens), seq, 3, np.array(lens), 8 + seq)
+
+
+def test_attention_more_work_items_than_sms(hom, cuda, oracle):
+    """32 x 16 heads x 2 tile pairs = 1024 items on 148 persistent CTAs: every CTA walks
+    several items and its K / V ring and barrier phases run on across item boundaries."""
+    lens = _rng(9).integers(256, 513, 32)
+    lens[3], lens[17] = 0, 1
+    _attention_case(hom, cuda, oracle, 32, 512, 16, lens, 9)
+
+
 def test_attention_rejects_head_dim(hom, cuda, pkg):
     import torch
     qkv = torch.zeros((1, 128, 3 * 2 * 32), dtype=torch.float16, device=cuda)
