@@ -242,6 +242,30 @@ row_stats_f16_kernel(const __half *x, __half *rstd_out, __half *shift_out, long 
   }
 }
 
+// Finaliser of the row statistics a GEMM epilogue left as per-column-group partial sums
+// (partials[g * rows + r] = {sum, sum of squares} of row r over columns [64 g, 64 g + 64)):
+// rstd = 1 / sqrt(E[x^2] - mean^2 + eps) and shift = -mean * rstd, stored as fp16 like the
+// reference's ApplyFinalReduction (include/NVGPUKernels/Layernorm.h:107-194).
+__global__ void __launch_bounds__(256)
+row_stats_finalize_kernel(const float2 *partials, int groups, long long rows, int n, float eps,
+                          __half *rstd_out, __half *shift_out) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
+  const long long r = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float sum = 0.f, sq = 0.f;
+  for (int g = 0; g < groups; ++g) {
+    const float2 v = partials[static_cast<long long>(g) * rows + r];
+    sum += v.x;
+    sq += v.y;
+  }
+  const float inv_n = 1.f / static_cast<float>(n);
+  const float mean = sum * inv_n;
+  const float rstd = rsqrtf(fmaxf(sq * inv_n - mean * mean, 0.f) + eps);
+  rstd_out[r] = __float2half_rn(rstd);
+  shift_out[r] = __float2half_rn(-mean * rstd);
+}
+
 // out[n] = sum_k b[k, n] (b is [K, N]) or sum_k b[n, k] (b is [N, K]), fp32.
 __global__ void __launch_bounds__(256)
 col_sum_f16_kernel(const __half *b, float *out, int k_dim, int n_dim, int b_is_nk) {
@@ -583,6 +607,16 @@ bool elementwise(int op, bool is_f16, const void *a, const void *b, void *out, i
     case 2: return elementwise_dispatch<2>(is_f16, a, b, out, n, b_period, sh, stream);
     default: return elementwise_dispatch<3>(is_f16, a, b, out, n, b_period, sh, stream);
   }
+}
+
+bool row_stats_finalize(const float2 *partials, int groups, int64_t rows, int64_t n, float eps, __half *rstd_out,
+                        __half *shift_out, cudaStream_t stream) {
+  if (rows == 0) return true;
+  LaunchScope scope(kOpLayernorm, 0.0, 8.0 * groups * rows + 4.0 * rows);
+  const unsigned blocks = static_cast<unsigned>((rows + 255) / 256);
+  return check_cuda(launch_pdl(row_stats_finalize_kernel, dim3(blocks), dim3(256), 0, stream, 1, partials, groups,
+                               static_cast<long long>(rows), static_cast<int>(n), eps, rstd_out, shift_out),
+                    "row statistics finaliser launch");
 }
 
 bool row_stats_f16(const __half *x, __half *rstd_out, __half *shift_out, int64_t rows, int64_t n,

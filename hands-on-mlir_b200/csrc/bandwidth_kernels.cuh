@@ -28,6 +28,10 @@ bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, flo
                    cudaStream_t stream);
 
 // rstd_out[r] = 1 / sqrt(E[x^2] - mean^2 + eps), shift_out[r] = -mean * rstd over each row of x.
+// Turns the per-64-column-group partial sums a GEMM epilogue left ([groups][rows] float2) into
+// rstd / -mean * rstd per row (fp16).
+bool row_stats_finalize(const float2 *partials, int groups, int64_t rows, int64_t n, float eps, __half *rstd_out,
+                        __half *shift_out, cudaStream_t stream);
 bool row_stats_f16(const __half *x, __half *rstd_out, __half *shift_out, int64_t rows, int64_t n,
                    float eps, cudaStream_t stream);
 // out[n] = sum over k of B[k, n] (or B[n, k] when b_is_nk), fp32.

@@ -135,7 +135,7 @@ bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, Spl
     b.counters = static_cast<int *>(ptr);
     b.counter_ints = want;
     b.clean_epoch = epoch;
-  } else if (b.clean_epoch != epoch) {
+  } else if (b.counters && b.clean_epoch != epoch) {
     // A kernel gave up a wait since these counters were last known clean.
     if (!check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize(split-K counters)")) return false;
     if (!check_cuda(cudaMemset(b.counters, 0, b.counter_ints * sizeof(int)), "cudaMemset(split-K counters)"))

@@ -32,6 +32,12 @@ struct EpilogueParams {
   // element by element and D is written by the warp from its staging tile with 4- or 2-byte
   // stores instead of a TMA store.
   int unaligned_n;
+  // Optional row statistics of D for a following LayerNorm (null when unused): every epilogue
+  // warp writes, per output row, the sum and the sum of squares of the fp16-rounded values of
+  // its 64-column group to row_partials[group * M + row] (group = column / 64); a small
+  // finalising kernel turns them into 1/sqrt(var + eps) and -mean/sqrt(var + eps).  This is what
+  // the reference's epilogue visitor does per N-tile (include/NVGPUKernels/Layernorm.h:409-479).
+  float2 *row_partials;
   // Diagnostics builds: bit mask that removes parts of the epilogue (1 accumulator read,
   // 2 arithmetic, 4 staging stores, 8 global store, 16 C read, 32 everything but the release).
   HOM_DIAG(int dbg;)
@@ -316,6 +322,27 @@ __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, co
                    "r"(w[2]), "r"(w[3])
                    : "memory");
     }
+  }
+  if (ep.row_partials != nullptr) {
+    // Each thread reads back the row it has just staged (its own writes: no barrier needed).
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int chunk = 0; chunk < 8; ++chunk) {
+      uint32_t w[4];
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                   : "r"(my_row + ((static_cast<uint32_t>(chunk) ^ (lane & 7u)) << 4))
+                   : "memory");
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 q = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+        const int col = c0 + chunk * 8 + 2 * j;
+        const float a = col < ep.N ? q.x : 0.f, b = col + 1 < ep.N ? q.y : 0.f;
+        s1 += a + b;
+        s2 = fmaf(a, a, fmaf(b, b, s2));
+      }
+    }
+    if (row < ep.M) ep.row_partials[static_cast<long long>(c0 >> 6) * ep.M + row] = make_float2(s1, s2);
   }
   if (!ep.unaligned_n) {
     fence_proxy_async_smem();

@@ -430,6 +430,7 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
+  p.ep.row_partials = pb.row_partials;
   HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
   p.ep.M = static_cast<int>(pb.M);
   p.ep.N = static_cast<int>(pb.N);

@@ -620,6 +620,7 @@ bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
+  p.ep.row_partials = pb.row_partials;
   HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>((pb.N + BN - 1) / BN);
@@ -699,6 +700,7 @@ bool launch_ln_variant(const Problem &pb, float eps, cudaStream_t stream) {
   p.ep.row_shift = nullptr;
   p.ep.col_sum = nullptr;
   p.ep.unaligned_n = 0;
+  p.ep.row_partials = nullptr;
   HOM_DIAG(p.ep.dbg = 0;)
   const int m_blocks = static_cast<int>((pb.M + BM - 1) / BM);
   p.n_blocks = static_cast<int>(pb.N / BN);
@@ -837,6 +839,7 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
+  p.ep.row_partials = pb.row_partials;
   HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
   p.b_grouped = grouped ? 1 : 0;
   p.b_early = pb.b_const ? 1 : 0;
@@ -1190,6 +1193,7 @@ bool run(const Problem &pb, int tile_row, cudaStream_t stream) {
   } else {
     split = pb.split_k >= 2 ? pb.split_k : 1;
   }
+  if (pb.row_partials) split = 1;  // the statistics come from the finished tile's epilogue
   const TileRow &t = kTileRows[tile_row];
   if (t.pair) return run_pair(pb, t.tile_n, split, stream);
   if (pb.b_is_nk) {

@@ -30,6 +30,9 @@ struct Problem {
   const __half *row_scale = nullptr;
   const __half *row_shift = nullptr;
   const float *col_sum = nullptr;
+  // When set: the epilogue also leaves per-row, per-64-column-group sums and sums of squares of
+  // D here ([ceil(N / 64)][M] float2), see EpilogueParams::row_partials.  Forces split_k = 1.
+  float2 *row_partials = nullptr;
 };
 
 // Enqueues the GEMM; tile_row 1..4 forces one CTA per 128 x {64,128,192,256} tile, 5..6 one

@@ -543,9 +543,12 @@ void cutlassGemmWithVarMeanF16(int64_t rankA, void *dstA, int64_t rankB, void *d
                                void *dstC, int64_t rankD, void *dstD, int64_t rankVar, void *dstVar,
                                int64_t rankMean, void *dstMean, float alpha, float beta,
                                int64_t activation, float eps) {
-  // D = alpha * A.B + beta * C, then per row of D: Var <- 1/sqrt(E[x^2] - mean^2 + eps) and
+  // D = alpha * A.B + beta * C, and per row of D: Var <- 1/sqrt(E[x^2] - mean^2 + eps) and
   // Mean <- -mean * Var (what the reference leaves in its first Bs*M entries after
-  // ApplyFinalReduction).  `activation` is ignored, as in the reference.
+  // ApplyFinalReduction).  Like the reference's epilogue visitor, the GEMM epilogue itself emits
+  // the per-row partial sums (fp32, one pair per 64-column group) while it still holds the tile;
+  // a small finaliser reduces them.  D is never read back.  `activation` is ignored, as in the
+  // reference.
   (void)activation;
   hom::gemm::Problem pb;
   bool empty = false;
@@ -556,8 +559,12 @@ void cutlassGemmWithVarMeanF16(int64_t rankA, void *dstA, int64_t rankB, void *d
   if (!stats_operand("cutlassGemmWithVarMeanF16", "Var", rankVar, dstVar, pb.M, &var) ||
       !stats_operand("cutlassGemmWithVarMeanF16", "Mean", rankMean, dstMean, pb.M, &mean))
     return;
+  const int groups = static_cast<int>((pb.N + 63) / 64);
+  hom::SplitWorkspace ws;  // library-owned scratch of this thread and stream
+  if (!hom::split_workspace(2 * static_cast<size_t>(groups) * pb.M, 0, hom::current_stream(), &ws)) return;
+  pb.row_partials = reinterpret_cast<float2 *>(ws.slots);
   if (!hom::gemm::run(pb, 0, hom::current_stream())) return;
-  hom::bw::row_stats_f16(pb.D, var, mean, pb.M, pb.N, eps, hom::current_stream());
+  hom::bw::row_stats_finalize(pb.row_partials, groups, pb.M, pb.N, eps, var, mean, hom::current_stream());
 }
 
 void cutlassLayernormGemmF32(int64_t, void *, int64_t, void *, int64_t, void *, int64_t, void *,

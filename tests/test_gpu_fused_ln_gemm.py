@@ -64,6 +64,29 @@ def test_against_oracle(hom, cuda, oracle, shape):
     assert_close_f16(d2.reshape(-1, n2)[rows], want2, "D2", rtol=2e-3, atol=2e-3)
 
 
+def test_statistics_come_from_the_gemm_epilogue(hom, cuda, oracle):
+    """cutlassGemmWithVarMeanF16 is the GEMM plus one small finaliser over the per-64-column
+    partial sums the GEMM's epilogue wrote (the reference's EpilogueVisitorLayerNorm +
+    ApplyFinalReduction, include/NVGPUKernels/Layernorm.h:107-194, 409-479): two launches, no
+    pass over D; M and N tails (N % 64 != 0) included."""
+    import torch
+    for (m, n, k) in [(300, 264, 72), (129, 104, 64), (4096, 768, 768)]:
+        rng = np.random.Generator(np.random.PCG64(3 + n))
+        A = f16(rng.normal(0, 1, (1, m, k)))
+        var = torch.full((m,), float("nan"), dtype=torch.float16, device=cuda)
+        mean = torch.full((m,), float("nan"), dtype=torch.float16, device=cuda)
+        D = torch.empty((1, m, n), dtype=torch.float16, device=cuda)
+        B = f16(rng.normal(0, 0.05, (1, k, n)))
+        before = hom.launch_count()
+        hom.cutlassGemmWithVarMeanF16(to_dev(A, cuda), to_dev(B, cuda), None, D, var, mean, 1.0, 0.0, 0, 1e-5)
+        assert hom.launch_count() - before == 2
+        hom.synchronize()
+        d = D.cpu().numpy()
+        w_var, w_mean = oracle.row_stats_f16(d, 1e-5)
+        assert_close_f16(var.cpu().numpy(), w_var, f"Var {m}x{n}", rtol=2e-3, atol=2e-3)
+        assert_close_f16(mean.cpu().numpy(), w_mean, f"Mean {m}x{n}", rtol=2e-3, atol=2e-3)
+
+
 def test_rejects_bad_statistics_operands(hom, cuda, pkg):
     import torch
     A = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
