@@ -266,6 +266,21 @@ row_stats_finalize_kernel(const float2 *partials, int groups, long long rows, in
   shift_out[r] = __float2half_rn(-mean * rstd);
 }
 
+// dst[r, c] = src[r, c] for c < cols, 0 for cols <= c < dst_pitch: a row-major matrix copied to a
+// larger row pitch (2-byte accesses: neither side's rows need any alignment).
+__global__ void __launch_bounds__(256)
+repitch_rows_f16_kernel(const __half *src, __half *dst, long long rows, int cols, int dst_pitch) {
+  hom::ptx::pdl_launch_dependents();
+  hom::ptx::pdl_wait();
+  const long long total = rows * dst_pitch;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / dst_pitch;
+    const int c = static_cast<int>(i - r * dst_pitch);
+    dst[i] = c < cols ? src[r * cols + c] : __float2half(0.f);
+  }
+}
+
 // out[n] = sum_k b[k, n] (b is [K, N]) or sum_k b[n, k] (b is [N, K]), fp32.
 __global__ void __launch_bounds__(256)
 col_sum_f16_kernel(const __half *b, float *out, int k_dim, int n_dim, int b_is_nk) {
@@ -607,6 +622,17 @@ bool elementwise(int op, bool is_f16, const void *a, const void *b, void *out, i
     case 2: return elementwise_dispatch<2>(is_f16, a, b, out, n, b_period, sh, stream);
     default: return elementwise_dispatch<3>(is_f16, a, b, out, n, b_period, sh, stream);
   }
+}
+
+bool repitch_rows_f16(const __half *src, __half *dst, int64_t rows, int64_t cols, int64_t dst_pitch,
+                      cudaStream_t stream) {
+  if (rows == 0 || dst_pitch == 0) return true;
+  LaunchScope scope(kOpElementwise, 0.0, 2.0 * rows * (cols + dst_pitch));
+  const long long total = rows * dst_pitch;
+  const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 148 * 16));
+  return check_cuda(launch_pdl(repitch_rows_f16_kernel, dim3(blocks), dim3(256), 0, stream, 1, src, dst,
+                               static_cast<long long>(rows), static_cast<int>(cols), static_cast<int>(dst_pitch)),
+                    "row re-pitch kernel launch");
 }
 
 bool row_stats_finalize(const float2 *partials, int groups, int64_t rows, int64_t n, float eps, __half *rstd_out,

@@ -28,6 +28,9 @@ bool layernorm_f32(const float *x, float *out, int64_t rows, int64_t hidden, flo
                    cudaStream_t stream);
 
 // rstd_out[r] = 1 / sqrt(E[x^2] - mean^2 + eps), shift_out[r] = -mean * rstd over each row of x.
+// dst [rows, dst_pitch] <- src [rows, cols] (row-major, zero padding), for any cols.
+bool repitch_rows_f16(const __half *src, __half *dst, int64_t rows, int64_t cols, int64_t dst_pitch,
+                      cudaStream_t stream);
 // Turns the per-64-column-group partial sums a GEMM epilogue left ([groups][rows] float2) into
 // rstd / -mean * rstd per row (fp16).
 bool row_stats_finalize(const float2 *partials, int groups, int64_t rows, int64_t n, float eps, __half *rstd_out,

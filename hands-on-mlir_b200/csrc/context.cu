@@ -147,6 +147,30 @@ bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, Spl
   return true;
 }
 
+namespace {
+struct PaddedKey {
+  uintptr_t ptr;
+  int64_t k, n;
+  bool operator<(const PaddedKey &o) const {
+    return ptr != o.ptr ? ptr < o.ptr : k != o.k ? k < o.k : n < o.n;
+  }
+};
+std::map<PaddedKey, __half *> g_padded_weights;  // guarded by g_const_mutex
+}  // namespace
+
+const __half *padded_weight_lookup(const void *ptr, int64_t k, int64_t n) {
+  std::lock_guard<std::mutex> lock(g_const_mutex);
+  auto it = g_padded_weights.find(PaddedKey{reinterpret_cast<uintptr_t>(ptr), k, n});
+  return it == g_padded_weights.end() ? nullptr : it->second;
+}
+
+void padded_weight_insert(const void *ptr, int64_t k, int64_t n, __half *copy) {
+  std::lock_guard<std::mutex> lock(g_const_mutex);
+  __half *&slot = g_padded_weights[PaddedKey{reinterpret_cast<uintptr_t>(ptr), k, n}];
+  if (slot) cudaFree(slot);
+  slot = copy;
+}
+
 void declare_constant_range(const void *ptr, size_t bytes) {
   if (!ptr || bytes == 0) return;
   const uintptr_t b = reinterpret_cast<uintptr_t>(ptr);
@@ -156,7 +180,15 @@ void declare_constant_range(const void *ptr, size_t bytes) {
 
 void forget_constant_range(const void *ptr) {
   std::lock_guard<std::mutex> lock(g_const_mutex);
-  g_const_ranges.erase(reinterpret_cast<uintptr_t>(ptr));
+  const uintptr_t b = reinterpret_cast<uintptr_t>(ptr);
+  auto range = g_const_ranges.find(b);
+  const uintptr_t e = range == g_const_ranges.end() ? b + 1 : range->second;
+  if (range != g_const_ranges.end()) g_const_ranges.erase(range);
+  // re-pitched copies of weights inside the withdrawn range go with it
+  for (auto it = g_padded_weights.lower_bound(PaddedKey{b, 0, 0}); it != g_padded_weights.end() && it->first.ptr < e;) {
+    cudaFree(it->second);
+    it = g_padded_weights.erase(it);
+  }
 }
 
 bool is_constant_range(const void *ptr, size_t bytes) {

@@ -413,7 +413,7 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   } else if (grouped) {
     if (!make_tensor_map_grouped(pb.B, pb.N, pb.K, BK, Cfg::kHalfN / 64, &tmB)) return false;
   } else {
-    if (!make_tensor_map_2d(pb.B, pb.N, pb.K, 64, BK, &tmB)) return false;
+    if (!make_tensor_map_2d(pb.B, pb.N, pb.K, 64, BK, &tmB, pb.ldb)) return false;
   }
   PairParams p;
   p.b_grouped = grouped ? 1 : 0;

@@ -406,9 +406,10 @@ struct MapKey {
   const void *ptr;
   uint64_t inner, outer;
   uint32_t box_inner, box_outer;  // box_outer | groups << 16 for the grouped 3-D form
+  uint64_t pitch;                 // row pitch in elements (== inner unless the rows are padded)
   bool operator==(const MapKey &o) const {
     return ptr == o.ptr && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
-           box_outer == o.box_outer;
+           box_outer == o.box_outer && pitch == o.pitch;
   }
 };
 struct MapKeyHash {
@@ -417,6 +418,7 @@ struct MapKeyHash {
     h = h * 1000003u ^ k.inner;
     h = h * 1000003u ^ k.outer;
     h = h * 1000003u ^ (static_cast<size_t>(k.box_inner) << 16 | k.box_outer);
+    h = h * 1000003u ^ k.pitch;
     return h;
   }
 };
@@ -482,10 +484,12 @@ void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStrea
 }
 #endif  // HOM_DIAG_ENABLED
 
-// 2-D fp16 tensor [outer, inner] (inner contiguous), 128-byte swizzle, zero fill.
+// 2-D fp16 tensor [outer, inner] (inner contiguous, rows `pitch` elements apart; 0 = inner),
+// 128-byte swizzle, zero fill.
 bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                        uint32_t box_outer, CUtensorMap *out) {
-  MapKey key{ptr, inner, outer, box_inner, box_outer};
+                        uint32_t box_outer, CUtensorMap *out, uint64_t pitch) {
+  if (pitch == 0) pitch = inner;
+  MapKey key{ptr, inner, outer, box_inner, box_outer, pitch};
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
     auto it = g_map_cache.find(key);
@@ -500,7 +504,7 @@ bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_
     return false;
   }
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {inner * 2};
+  cuuint64_t strides[1] = {pitch * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t elem_strides[2] = {1, 1};
   CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims,
@@ -525,7 +529,7 @@ bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_
 // TMA instruction fetches what would otherwise take one 2-D load per 64-column group.
 bool make_tensor_map_grouped(const void *ptr, uint64_t cols, uint64_t rows, uint32_t box_rows,
                              uint32_t groups, CUtensorMap *out) {
-  MapKey key{ptr, cols, rows, 64u | 0x80000000u, box_rows | (groups << 16)};
+  MapKey key{ptr, cols, rows, 64u | 0x80000000u, box_rows | (groups << 16), cols};
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
     auto it = g_map_cache.find(key);
@@ -600,7 +604,7 @@ bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   } else if (grouped) {
     if (!make_tensor_map_grouped(pb.B, pb.N, pb.K, BK, BN / 64, &tmB)) return false;
   } else {
-    if (!make_tensor_map_2d(pb.B, pb.N, pb.K, 64, BK, &tmB)) return false;
+    if (!make_tensor_map_2d(pb.B, pb.N, pb.K, 64, BK, &tmB, pb.ldb)) return false;
   }
   Params p;
   p.b_grouped = grouped ? 1 : 0;

@@ -14,6 +14,9 @@ struct Problem {
   const __half *A = nullptr;    // [M, K]
   const __half *B = nullptr;    // [K, N], or [N, K] when b_is_nk
   bool b_is_nk = false;
+  // Row pitch of B stored [K, N], in elements (0 = N).  A pitch that is a multiple of 8 lets TMA
+  // fetch a B whose N is not (the vocabulary projection, N = 30522).
+  int64_t ldb = 0;
   // B lies in a declared constant range: its first tiles may be requested before the previous
   // kernel of the stream has finished.
   bool b_const = false;
@@ -78,7 +81,7 @@ void profile_report(const char *what, int tiles, int grid, int num_kb, cudaStrea
 
 // Cached cuTensorMapEncodeTiled for a 2-D fp16 tensor [outer, inner], 128-byte swizzle.
 bool make_tensor_map_2d(const void *ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                        uint32_t box_outer, CUtensorMap *out);
+                        uint32_t box_outer, CUtensorMap *out, uint64_t pitch = 0);
 
 // Row-major [rows, cols] fp16 matrix, cols % 64 == 0, as (64, rows, cols/64): one box of
 // (64, box_rows, groups) becomes `groups` consecutive swizzled [box_rows x 64] sub-tiles.

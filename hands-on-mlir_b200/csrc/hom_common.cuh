@@ -78,6 +78,12 @@ cudaStream_t current_stream();
 void declare_constant_range(const void *ptr, size_t bytes);
 void forget_constant_range(const void *ptr);
 bool is_constant_range(const void *ptr, size_t bytes);
+// Library-owned copies of declared-constant [K, N] weights whose N is not a multiple of 8,
+// re-laid-out with an 8-element-aligned row pitch so that TMA can fetch them; keyed on the
+// original pointer and shape, dropped when the declaration is withdrawn.  lookup returns null
+// when there is none yet; insert takes ownership of a cudaMalloc'ed copy.
+const __half *padded_weight_lookup(const void *ptr, int64_t k, int64_t n);
+void padded_weight_insert(const void *ptr, int64_t k, int64_t n, __half *copy);
 // Programmatic dependent launch is on unless HOM_DISABLE_PDL is set (diagnostics).
 bool pdl_enabled();
 // Host-mapped status word that device code writes on a bounded-wait expiry (device pointer).

@@ -240,7 +240,8 @@ void dealloc_memref(int64_t rank, void *dst) {
 // is rejected (error recorded) or there is nothing to do (M or N is 0: *empty set).
 bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64_t rankB,
                   void *dstB, int64_t rankC, void *dstC, int64_t rankD, void *dstD,
-                  int64_t activation, float alpha, float beta, hom::gemm::Problem *out, bool *empty) {
+                  int64_t activation, float alpha, float beta, hom::gemm::Problem *out, bool *empty,
+                  bool allow_unaligned_kn = false) {
   *empty = false;
   MemRefView A = view_memref(rankA, dstA, 2), B = view_memref(rankB, dstB, 2);
   MemRefView C = view_memref(rankC, dstC, 2), D = view_memref(rankD, dstD, 2);
@@ -295,7 +296,7 @@ bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int
   }
   // TMA needs 16-byte rows: K % 8 == 0 for A (and for B stored [N,K]); N % 8 == 0 for B
   // stored [K,N].  With B as [N,K] any N works: C / D are then handled without TMA.
-  if (K % 8 != 0 || (!b_is_nk && N % 8 != 0)) {
+  if (K % 8 != 0 || (!b_is_nk && N % 8 != 0 && !allow_unaligned_kn)) {
     set_error(HOM_ERR_UNSUPPORTED,
               "%s: K%s must be a multiple of 8 (16-byte rows for TMA); got K=%lld N=%lld", name,
               b_is_nk ? "" : " and N", static_cast<long long>(K), static_cast<long long>(N));
@@ -339,11 +340,63 @@ bool gemm_prepare(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int
       return false;
     }
   }
-  if (!is_aligned16(pb.A) || !is_aligned16(pb.B) || (!unaligned_n && !is_aligned16(pb.D))) {
+  if (!is_aligned16(pb.A) || (!(unaligned_n && !b_is_nk) && !is_aligned16(pb.B)) ||
+      (!unaligned_n && !is_aligned16(pb.D))) {
     set_error(HOM_ERR_INVALID, "%s: A, B and D must be 16-byte aligned", name);
     return false;
   }
   *out = pb;
+  return true;
+}
+
+// B stored [K, N] with N % 8 != 0 (the vocabulary projection, N = 30522, which the reference
+// serves with alignment-2 kernels, python/gemm_generator.py:232): its rows are not 16-byte
+// aligned, so TMA cannot fetch it in place.  The GEMM runs on a copy whose row pitch is rounded
+// up to 8 elements: made once and kept for a declared constant (model weights), re-made on every
+// call into a grow-only scratch of the calling thread for any other B.
+bool repitch_unaligned_b(const char *name, hom::gemm::Problem *pb) {
+  const int64_t pitch = (pb->N + 7) / 8 * 8;
+  cudaStream_t stream = hom::current_stream();
+  const __half *copy = pb->b_const ? hom::padded_weight_lookup(pb->B, pb->K, pb->N) : nullptr;
+  if (!copy) {
+    __half *fresh = nullptr;
+    if (pb->b_const) {
+      void *ptr = nullptr;
+      if (!hom::check_cuda(cudaMalloc(&ptr, static_cast<size_t>(pb->K) * pitch * 2), "cudaMalloc(re-pitched weights)"))
+        return false;
+      fresh = static_cast<__half *>(ptr);
+    } else {
+      thread_local __half *scratch = nullptr;
+      thread_local size_t scratch_elems = 0;
+      const size_t need = static_cast<size_t>(pb->K) * pitch;
+      if (scratch_elems < need) {
+        if (scratch) cudaFree(scratch);  // waits for the kernels that may still read it
+        scratch = nullptr;
+        scratch_elems = 0;
+        void *ptr = nullptr;
+        if (!hom::check_cuda(cudaMalloc(&ptr, need * 2), "cudaMalloc(re-pitched B)")) return false;
+        scratch = static_cast<__half *>(ptr);
+        scratch_elems = need;
+      }
+      fresh = scratch;
+    }
+    if (!hom::bw::repitch_rows_f16(pb->B, fresh, pb->K, pb->N, pitch, stream)) {
+      if (pb->b_const) cudaFree(fresh);
+      return false;
+    }
+    if (pb->b_const) {
+      // other streams may use the cached copy next: make it complete before it becomes visible
+      if (!hom::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize(re-pitched weights)")) {
+        cudaFree(fresh);
+        return false;
+      }
+      hom::padded_weight_insert(pb->B, pb->K, pb->N, fresh);
+    }
+    copy = fresh;
+  }
+  (void)name;
+  pb->B = copy;
+  pb->ldb = pitch;
   return true;
 }
 
@@ -354,8 +407,9 @@ void gemm_entry(const char *name, bool b_is_nk, int64_t rankA, void *dstA, int64
   hom::gemm::Problem pb;
   bool empty = false;
   if (!gemm_prepare(name, b_is_nk, rankA, dstA, rankB, dstB, rankC, dstC, rankD, dstD, activation,
-                    alpha, beta, &pb, &empty))
+                    alpha, beta, &pb, &empty, /*allow_unaligned_kn=*/true))
     return;
+  if (!b_is_nk && pb.N % 8 != 0 && !repitch_unaligned_b(name, &pb)) return;
   pb.split_k = split_k;
   hom::gemm::run(pb, tile_row, hom::current_stream());
 }

@@ -253,7 +253,12 @@ def test_batch_composition_does_not_change_a_sequence(hom, cuda, oracle):
     for b in (1, 4):
         prog1, alone, _ = run_case(hom, cuda, oracle, cfg, w, ids[b:b + 1], mask[b:b + 1], types[b:b + 1])
         prog1.close()
-        assert_end_to_end_close(alone[0, :lens[b]], full[b, :lens[b]], f"sequence {b} alone vs in a batch of 6")
+        # Not bit-identical: the GEMM tile shape and K split are chosen per problem size, so the
+        # fp32 summation order differs between M = 512 and M = 3072 (measured: 0.13 % of the
+        # elements differ by more than rtol/atol 1e-3 after three layers, 4e-6 by more than 2e-3;
+        # both runs are equally close to the oracle).
+        f1, f2, fref = drift_fractions(alone[0, :lens[b]], full[b, :lens[b]])
+        assert f1 <= 5e-3 and f2 <= 1e-4 and fref == 0.0, (b, f1, f2, fref)
 
 
 def test_graph_replay_and_host_entry_point_are_bit_identical(hom, cuda, oracle):

@@ -195,13 +195,46 @@ def test_nvte_gemm_n_not_multiple_of_8(hom, cuda, oracle, shape, act, beta):
     assert_close_f16(got, oracle.gemm_f16(A, B, C, b_is_nk=True, act=act, beta=beta), f"nvte odd N {shape}")
 
 
-def test_cutlass_layout_rejects_n_not_multiple_of_8(hom, cuda, pkg):
+@pytest.mark.parametrize("shape,act,beta", [((1, 128, 100, 64), 0, 0.0), ((2, 100, 30, 72), 1, 0.0),
+                                            ((1, 64, 31, 64), 0, 1.0), ((3, 130, 1001, 136), 0, 1.0),
+                                            ((1, 256, 30522, 768), 0, 0.0)])
+@pytest.mark.parametrize("declared", [False, True])
+def test_cutlass_gemm_n_not_multiple_of_8(hom, cuda, oracle, shape, act, beta, declared):
+    """B as [1,K,N] with N % 8 != 0 through cutlassGemmF16 (the autotuned vocabulary projection,
+    N = 30522: the reference generates alignment-2 kernels for it, python/gemm_generator.py:232,
+    examples/torch/bert/bert.cu:25,140).  B's rows are not 16-byte aligned: the GEMM runs on a
+    copy with a padded row pitch - cached when B is a declared weight, remade per call when not."""
+    bs, m, n, k = shape
+    rng = _rng(14)
+    A = rng.uniform(-1, 1, (bs, m, k)).astype(np.float16)
+    B = rng.normal(0, 0.03, (1, k, n)).astype(np.float16)
+    C = rng.normal(0, 1, (bs, m, n)).astype(np.float16) if beta else None
+    want = oracle.gemm_f16(A, B, C, act=act, beta=beta)
+    import torch
+    tA, tB = to_dev(A, cuda), to_dev(B, cuda)
+    if declared:
+        hom.declare_weights(tB)
+    try:
+        for rep in range(2):  # the second call of a declared B uses the cached copy
+            tD = to_dev(C, cuda) if beta else torch.full((bs, m, n), float("nan"), dtype=torch.float16, device=cuda)
+            hom.cutlassGemmF16(tA, tB, tD, tD, activation=act, beta=beta)
+            hom.synchronize()
+            assert_close_f16(tD.cpu().numpy(), want, f"[K,N] odd N {shape} declared={declared} call {rep}")
+    finally:
+        if declared:
+            hom.forget_weights(tB)
+
+
+def test_statistics_entry_points_still_need_n_multiple_of_8(hom, cuda, pkg):
+    """The GEMM <-> LayerNorm-statistics pair keeps the 16-byte row rule (the reference only
+    instantiates it at alignment 8)."""
     import torch
     A = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
     B = torch.zeros((1, 64, 100), dtype=torch.float16, device=cuda)
     D = torch.zeros((1, 128, 100), dtype=torch.float16, device=cuda)
+    v = torch.zeros((128,), dtype=torch.float16, device=cuda)
     with pytest.raises(pkg.HomError) as e:
-        hom.cutlassGemmF16(A, B, D, D)
+        hom.cutlassGemmWithVarMeanF16(A, B, D, D, v, v)
     assert e.value.code == 2
 
 
@@ -241,10 +274,10 @@ def test_gemm_rejects_bad_arguments(hom, cuda, pkg):
     with pytest.raises(pkg.HomError) as e:
         hom.cutlassGemmF16(A, B, D, D)
     assert e.value.code == 1
-    B2 = torch.zeros((1, 64, 60), dtype=torch.float16, device=cuda)  # N % 8 != 0
-    D2 = torch.zeros((1, 128, 60), dtype=torch.float16, device=cuda)
+    A3 = torch.zeros((1, 128, 60), dtype=torch.float16, device=cuda)  # K % 8 != 0
+    B3 = torch.zeros((1, 60, 64), dtype=torch.float16, device=cuda)
     with pytest.raises(pkg.HomError) as e:
-        hom.cutlassGemmF16(A, B2, D2, D2)
+        hom.cutlassGemmF16(A3, B3, D, D)
     assert e.value.code == 2
     with pytest.raises(pkg.HomError):
         hom.nvteGemmF16(A, B, D, D, transb=False)
