@@ -433,12 +433,15 @@ class Ranks:
         return float(t.item())
 
 
-def timed_region(ranks, stream, step, steps: int, min_seconds: float = MIN_TIMED_SECONDS):
+def timed_region(ranks, stream, step, steps: int, min_seconds: float | None = None):
     """Times `steps` calls of `step()` per round, as many rounds back to back as it takes to fill
     `min_seconds` (the same number on every rank), between two CUDA events on the launching
     stream with a barrier + synchronize on both sides.  Returns (ms per step = max over ranks of
     the whole region / steps run, steps run, seconds)."""
     import torch
+    if min_seconds is None:
+        min_seconds = MIN_TIMED_SECONDS
+    min_seconds = min(min_seconds, MIN_TIMED_SECONDS)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ranks.barrier()
     ev0.record(stream)
@@ -868,6 +871,58 @@ def run_gpu_arm(args, cfg, workload):
         dist.destroy_process_group()
 
 
+def run_grid_arm(args):
+    """The reference's own benchmark grid (examples/torch/bert/benchmark_bert.py:50-52: batch
+    {1, 8, 16, 32} x seq {64, 128}) for BERT-base and BERT-large on one GPU: CUDA-graph replay,
+    inputs in HBM, >= 0.3 s per cell; prints one JSON line with a row per cell, each with the
+    tile-table row and K split the library picked for the layer's four GEMM shapes."""
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from hands_on_mlir_b200.bert_program import BertConfig, BertProgram
+    hom = pkg.runner()
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    hom.use_torch_stream()
+    ranks = Ranks(device)
+    rows = []
+    for model, cfg in (("bert-base", BertConfig.base()), ("bert-large", BertConfig.large())):
+        for seq in (64, 128):
+            weights = make_weights_torch(cfg, seq, device)
+            for batch in (1, 8, 16, 32):
+                wl = dict(model=model, batch=batch, seq=seq, scaling="weak", lens=None)
+                prog = BertProgram(cfg, batch, seq)
+                prog.set_weights(weights)
+                ids, mask, types = (torch.from_numpy(x).to(device) for x in make_inputs(wl, batch, 0))
+                for _ in range(3):
+                    prog.forward(ids, mask, types, use_graph=True)
+                hom.synchronize()
+                ms, n_run, _ = timed_region(ranks, stream, lambda: prog.forward(ids, mask, types, use_graph=True),
+                                            20, min_seconds=0.3)
+                for _ in range(3):
+                    prog.forward(ids, mask, types, use_graph=False)
+                hom.synchronize()
+                ms_e, _, _ = timed_region(ranks, stream, lambda: prog.forward(ids, mask, types, use_graph=False),
+                                          20, min_seconds=0.2)
+                m, h, f = batch * seq, cfg.hidden, cfg.ffn
+                shapes = {"qkv": (m, 3 * h, h, 0), "out": (m, h, h, 0), "ffn1": (m, f, h, 1), "ffn2": (m, h, f, 0)}
+                tiles = {}
+                for name, shp in shapes.items():
+                    q = hom.gemm_query_tile(*shp)
+                    tiles[name] = f"row {q['row']} ({'256' if q['row'] >= 5 else '128'}x{q['bn']}), split {q['split_k']}"
+                flops = (cfg.gemm_flops_per_sequence(seq) + cfg.attention_flops_per_sequence(seq)) * batch
+                rows.append({"model": model, "batch": batch, "seq": seq, "ms_per_step": ms,
+                             "sequences_per_s": batch / (ms / 1e3), "model_tflops": flops / (ms / 1e3) / 1e12,
+                             "eager_ms_per_step": ms_e, "steps_timed": n_run, "gemm_tiles": tiles})
+                prog.close()
+            del weights
+    print(json.dumps({"metric": "bert_fp16_sequences_per_s", "unit": "sequences/s", "n_gpus": 1,
+                      "grid": "batch {1, 8, 16, 32} x seq {64, 128}, bert-base and bert-large, CUDA-graph replay",
+                      "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -894,9 +949,20 @@ def main():
     ap.add_argument("--shape", default=None, help="with --op gemm-*: override M,N,K")
     ap.add_argument("--l2-resident", action="store_true",
                     help="with --op: reuse one buffer set (L2-resident figure)")
+    ap.add_argument("--min-seconds", type=float, default=None,
+                    help="GPU time every throughput figure is averaged over (default 1.0; lower it only "
+                         "for a profiler capture, whose numbers are never bench values)")
+    ap.add_argument("--grid", action="store_true",
+                    help="time the reference's benchmark grid (batch 1/8/16/32 x seq 64/128, base and large)")
     args = ap.parse_args()
+    if args.min_seconds is not None:
+        global MIN_TIMED_SECONDS
+        MIN_TIMED_SECONDS = max(0.0, args.min_seconds)
     if args.op:
         run_op_arm(args)
+        return
+    if args.grid:
+        run_grid_arm(args)
         return
 
     from __graft_entry__ import load_package
