@@ -57,14 +57,14 @@ WORKLOADS = {
 # over the 48 GEMM launches of one step with caches as the preceding kernels leave them.
 NCU_TRAFFIC_BYTES = {
     "bert-base": {"bytes": 8.32e6, "source": "profiles/launch_list_bert_base_b32_s128.txt"},
-    "gemm-ffn1": {"bytes": 11.07e6, "source": "profiles/gemm_pair_256x256_bert_base_ffn1.txt"},
+    "gemm-ffn1": {"bytes": 11.09e6, "source": "profiles/gemm_pair_256x256_bert_base_ffn1.txt"},
     "gemm-qkv": {"bytes": 9.89e6, "source": "profiles/gemm_pair_256x256_bert_base_qkv.txt"},
-    "gemm-ffn2": {"bytes": 36.24e6, "source": "profiles/gemm_1cta_128x192_bert_base_ffn2.txt"},
+    "gemm-ffn2": {"bytes": 36.25e6, "source": "profiles/gemm_1cta_128x192_bert_base_ffn2.txt"},
     "gemm-large-ffn1": {"bytes": 122.0e6, "source": "profiles/gemm_pair_256x256_bert_large_ffn1_m16384.txt"},
     "ln-c2": {"bytes": 12.60e6, "source": "profiles/layernorm_residual_affine_4096x768.txt"},
     "ln-large": {"bytes": 480.6e6, "source": "profiles/layernorm_inplace_131072x1024.txt"},
     "attn-c3": {"bytes": 18.90e6, "source": "profiles/attention_single_tile_bs32_seq128_h12.txt"},
-    "attn-large": {"bytes": 105.8e6, "source": "profiles/attention_multi_tile_bs32_seq512_h16.txt"},
+    "attn-large": {"bytes": 101.6e6, "source": "profiles/attention_two_query_tiles_bs32_seq512_h16.txt"},
 }
 
 
