@@ -842,7 +842,8 @@ def run_gpu_arm(args, cfg, workload):
                       "activations) exceeds the 126 MB L2",
                 "launch": "CUDA-graph replay of the runner-utils call sequence"
                           + (" with the fused embedding extension" if args.fused_embedding else "")
-                          + (" with the fused GEMM+LayerNorm extension" if args.fused_layernorm else ""),
+                          + (" with the deferred-LayerNorm extension" if args.fused_layernorm == 2 else
+                             " with the fused GEMM+LayerNorm extension" if args.fused_layernorm else ""),
                 "timing": f"{args.steps}-step rounds repeated back to back for >= {MIN_TIMED_SECONDS:.0f} s "
                           "between one pair of CUDA events; ms_per_step is the mean over all of them",
             },
@@ -933,10 +934,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-config5", action="store_true",
                     help="skip the bert-large (batch 256 x seq 512, split over the GPUs) sub-record")
-    ap.add_argument("--fused-layernorm", action="store_true",
-                    help="replace the GEMM + LayerNorm call pairs (out-projection, FFN2) by "
-                         "homGemmResidualLayernormF16 (an extension; off by default like "
-                         "--fused-embedding)")
+    ap.add_argument("--fused-layernorm", type=int, nargs="?", const=2, default=0, choices=[0, 1, 2],
+                    help="extensions, off by default like --fused-embedding: 2 (the flag alone) = deferred "
+                         "LayerNorm, every GEMM applies the LayerNorm of its operands in its epilogue "
+                         "(homGemmDeferredLayernormF16, no LayerNorm launch inside the layers); 1 = "
+                         "homGemmResidualLayernormF16 in place of the GEMM + LayerNorm call pairs")
     ap.add_argument("--fused-embedding", action="store_true",
                     help="replace the five embedding calls by homBertEmbeddingF16 (same bits; not "
                          "the call sequence the reference's lowering emits, so off by default)")

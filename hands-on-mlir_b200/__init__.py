@@ -145,6 +145,7 @@ _SIGNATURES = {
     "homBertEmbeddingF16": (None, _MEMREF * 6 + [c_float]),
     "homGemmResidualLayernormF16": (None, _MEMREF * 2 + [ctypes.c_bool] + _MEMREF * 2 + [c_float]),
     "homLayernormGemmF16NoAlloc": (None, _MEMREF * 6 + [c_float, c_float]),
+    "homGemmDeferredLayernormF16": (None, _MEMREF * 3 + [ctypes.c_bool] + _MEMREF * 4 + [c_int64, c_float]),
     "homKernelLaunchCount": (c_int64, []),
     "homOpTimingEnable": (None, [ctypes.c_int]),
     "homOpTimingCollect": (c_int64, [ctypes.POINTER(OpTiming), c_int64]),
@@ -255,6 +256,13 @@ class RunnerUtils:
 
     def nvteLayernormF32(self, A, eps=1e-6):
         self.lib.nvteLayernormF32(*_as_args(A), eps)
+        self.check()
+
+    def homGemmDeferredLayernormF16(self, A, statsA, B, R, statsR, D, statsD, activation=0, eps=1e-12,
+                                    weights_nk=False):
+        self.lib.homGemmDeferredLayernormF16(*_as_args(A), *_as_args(statsA), *_as_args(B), weights_nk,
+                                             *_as_args(R), *_as_args(statsR), *_as_args(D),
+                                             *_as_args(statsD), activation, eps)
         self.check()
 
     def homResidualLayernormF16(self, X, R, gamma, beta, Out, eps=1e-12):

@@ -112,7 +112,7 @@ class BertProgram:
     """One replay program: a model configuration at a fixed [batch, seq] on the current GPU."""
 
     def __init__(self, cfg: BertConfig, batch: int, seq: int, weights_nk: bool = False,
-                 fused_embedding: bool = False, fused_layernorm: bool = False):
+                 fused_embedding: bool = False, fused_layernorm: bool | int = False):
         self.cfg, self.batch, self.seq, self.weights_nk = cfg, batch, seq, weights_nk
         self.fused_embedding, self.fused_layernorm = fused_embedding, fused_layernorm
         self._lib = _replay_lib()

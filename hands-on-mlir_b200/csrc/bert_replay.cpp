@@ -54,6 +54,7 @@ struct Program {
   HomBertConfig cfg{};
   std::vector<Tensor> weights;
   Tensor x, type_rows, qkv, ctx, ffn, cu;  // activations (hoisted allocations)
+  Tensor stats[2];  // fused_layernorm == 2: fp32 row partial sums of the raw hidden states (ping-pong)
   Tensor ids_dev, mask_dev, types_dev;     // staging for the host entry point
   cudaStream_t own_stream = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
@@ -70,6 +71,8 @@ struct Program {
   const void *host_graph_in[2][3] = {{nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr}};
   void *graph_ids = nullptr, *graph_mask = nullptr, *graph_types = nullptr;
   bool warmed_up = false;
+  cudaStream_t warm_stream = nullptr;  // the stream of the latest eager forward
+  bool warm_stream_valid = false;
 };
 
 void release(Tensor &t, bool f16) {
@@ -142,6 +145,36 @@ int issue_forward(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void
                             p.x.desc);
     nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
   }
+  if (c.fused_layernorm == 2) {
+    // Deferred LayerNorm (homGemmDeferredLayernormF16): from the first output projection on the
+    // residual stream `x` stays raw (un-normalised) and travels with the fp32 partial sums of
+    // its rows; every consumer applies the LayerNorm in its epilogue - the QKV and FFN1 GEMMs
+    // on their A operand, the output projection and FFN2 on their residual - and the two
+    // GEMMs that write `x` emit the partial sums of what they write.  No LayerNorm launch
+    // inside the layers; one at the very end normalises the last raw `x`.
+    Tensor none{};
+    int cur = -1;  // which stats buffer describes x (-1: x is normalised, no statistics)
+    auto deferred = [&](Tensor &a, Tensor &sa, Tensor &w, Tensor &r, Tensor &sr, Tensor &d, Tensor &sd,
+                        int64_t act) {
+      homGemmDeferredLayernormF16(a.rank, a.desc, sa.rank, sa.desc, w.rank, w.desc, c.weights_nk != 0, r.rank,
+                                  r.desc, sr.rank, sr.desc, d.rank, d.desc, sd.rank, sd.desc, act, c.eps);
+    };
+    for (int l = 0; l < c.layers; ++l) {
+      Tensor &wqkv = p.weights[3 + 4 * l], &wo = p.weights[4 + 4 * l];
+      Tensor &w1 = p.weights[5 + 4 * l], &w2 = p.weights[6 + 4 * l];
+      Tensor &s_in = cur < 0 ? none : p.stats[cur];
+      deferred(p.x, s_in, wqkv, none, none, p.qkv, none, 0);
+      nvteBertAttentionF16(p.qkv.rank, p.qkv.desc, p.cu.rank, p.cu.desc, p.ctx.rank, p.ctx.desc, scale,
+                           c.heads);
+      const int mid = cur < 0 ? 0 : cur ^ 1;
+      deferred(p.ctx, none, wo, p.x, s_in, p.x, p.stats[mid], 0);        // x <- ctx.Wo + LN(x), raw
+      deferred(p.x, p.stats[mid], w1, none, none, p.ffn, none, 1);       // GELU(LN(x).W1)
+      deferred(p.ffn, none, w2, p.x, p.stats[mid], p.x, p.stats[mid ^ 1], 0);  // x <- ffn.W2 + LN(x), raw
+      cur = mid ^ 1;
+    }
+    if (c.layers > 0) nvteLayernormF16(p.x.rank, p.x.desc, c.eps);
+    return status();
+  }
   for (int l = 0; l < c.layers; ++l) {
     Tensor &wqkv = p.weights[3 + 4 * l], &wo = p.weights[4 + 4 * l];
     Tensor &w1 = p.weights[5 + 4 * l], &w2 = p.weights[6 + 4 * l];
@@ -173,6 +206,8 @@ int forward_impl(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void 
     // The first call always runs eagerly: it performs the library's one-time set-up
     // (kernel attributes, tensor-map cache), which must not happen during capture.
     p.warmed_up = true;
+    p.warm_stream = static_cast<cudaStream_t>(homGetStream());
+    p.warm_stream_valid = true;
     return issue_forward(p, rankIds, ids, rankMask, mask, rankTypes, types);
   }
   cudaStream_t stream = static_cast<cudaStream_t>(homGetStream());
@@ -190,6 +225,17 @@ int forward_impl(Program &p, int64_t rankIds, void *ids, int64_t rankMask, void 
         return HOM_ERR_CUDA;
       stream = p.own_stream;
       homSetStream(stream);
+    }
+    if (p.warm_stream != stream || !p.warm_stream_valid) {
+      // Per-stream scratch of the library (the split-K workspace) is allocated on a stream's
+      // first use, which must not happen during capture: run once eagerly on this stream.
+      const int wrc = issue_forward(p, rankIds, ids, rankMask, mask, rankTypes, types);
+      if (wrc != 0) {
+        homSetStream(user_stream);
+        return wrc;
+      }
+      p.warm_stream = stream;
+      p.warm_stream_valid = true;
     }
     cudaGraph_t graph = nullptr;
     if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
@@ -238,6 +284,9 @@ void *homBertCreate(const HomBertConfig *cfg) {
   p->ctx = from_alloc(alloc3DMemRefNVGPUF16(b, s, h));
   p->ffn = from_alloc(alloc3DMemRefNVGPUF16(b, s, cfg->ffn));
   p->cu = from_alloc(alloc1DMemRefNVGPUI32(b + 1));
+  if (cfg->fused_layernorm == 2) {
+    for (int i = 0; i < 2; ++i) p->stats[i] = from_alloc(alloc3DMemRefNVGPUF32((h + 63) / 64, b * s, 2));
+  }
   // int64 staging for the host entry point: 3 x [b, s] carved from one I32 allocation.
   Tensor staging = from_alloc(alloc1DMemRefNVGPUI32(3 * 2 * b * s));
   if (status() != 0 || !p->x.data() || !p->type_rows.data() || !p->qkv.data() || !p->ctx.data() ||
@@ -280,6 +329,7 @@ void homBertDestroy(void *program) {
   release(p->ctx, true);
   release(p->ffn, true);
   release(p->cu, false);
+  for (int i = 0; i < 2; ++i) release(p->stats[i], false);  // fp32: the untyped device free
   release(p->mask_dev, false);
   release(p->types_dev, false);
   release(p->ids_dev, false);
@@ -417,10 +467,13 @@ int homBertForwardHostAsync(void *program, const int64_t *ids_host, const int64_
         static_cast<const uint4 *>(p->x.data()), static_cast<uint4 *>(p->result_slot[slot].data()),
         static_cast<long long>(out_bytes / 16));
     if (cudaGetLastError() != cudaSuccess) return HOM_ERR_CUDA;
-  } else if (!use_graph || !p->warmed_up || stream == nullptr) {
-    // eager: also the first call of a program (one-time set-up must not happen during capture)
-    // and the legacy default stream, which cannot be captured
+  } else if (!use_graph || !p->warmed_up || !p->warm_stream_valid || p->warm_stream != stream ||
+             stream == nullptr) {
+    // eager: also the first call of a program on this stream (one-time and per-stream set-up
+    // must not happen during capture) and the legacy default stream, which cannot be captured
     p->warmed_up = true;
+    p->warm_stream = stream;
+    p->warm_stream_valid = true;
     const int rc = issue_step();
     if (rc != 0) return rc;
   } else {
@@ -479,7 +532,10 @@ void homBertHostTraffic(void *program, int64_t *h2d_bytes, int64_t *d2h_bytes) {
 
 int32_t homBertLaunchesPerForward(void *program) {
   auto *p = static_cast<Program *>(program);
-  return p ? (p->cfg.fused_embedding ? 2 : 6) + (p->cfg.fused_layernorm ? 5 : 7) * p->cfg.layers : 0;
+  if (!p) return 0;
+  const int per_layer = p->cfg.fused_layernorm ? 5 : 7;
+  const int tail = p->cfg.fused_layernorm == 2 && p->cfg.layers > 0 ? 1 : 0;  // the final LayerNorm
+  return (p->cfg.fused_embedding ? 2 : 6) + per_layer * p->cfg.layers + tail;
 }
 
 }  // extern "C"

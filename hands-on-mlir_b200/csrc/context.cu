@@ -80,6 +80,9 @@ void set_error(int code, const char *fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(tl_error_text, sizeof(tl_error_text), fmt, ap);
   va_end(ap);
+  // The slot keeps the latest error only; HOM_TRACE_ERRORS=1 prints every one as it is set.
+  static const bool trace = std::getenv("HOM_TRACE_ERRORS") != nullptr;
+  if (trace) std::fprintf(stderr, "[hom error %d] %s\n", code, tl_error_text);
 }
 
 bool check_cuda(cudaError_t e, const char *what) {
@@ -111,7 +114,7 @@ bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, Spl
   if (b.slot_floats < slot_floats) {
     // Round up generously: the typical caller alternates between a few shapes.
     size_t want = slot_floats < (size_t{8} << 20) ? (size_t{8} << 20) : slot_floats + slot_floats / 2;
-    if (b.slots) cudaFree(b.slots);  // waits for the kernels that may still use it
+    // The outgrown buffer is kept, not freed: a captured graph may still hold its address.
     b.slots = nullptr;
     b.slot_floats = 0;
     void *ptr = nullptr;
@@ -123,8 +126,7 @@ bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, Spl
   const size_t ints = blocks;
   if (b.counter_ints < ints) {
     size_t want = ints < (size_t{1} << 16) ? (size_t{1} << 16) : 2 * ints;
-    if (b.counters) cudaFree(b.counters);
-    b.counters = nullptr;
+    b.counters = nullptr;  // kept, like the slots
     b.counter_ints = 0;
     void *ptr = nullptr;
     if (!check_cuda(cudaMalloc(&ptr, want * sizeof(int)), "cudaMalloc(split-K counters)")) return false;
@@ -150,26 +152,36 @@ bool split_workspace(size_t slot_floats, size_t blocks, cudaStream_t stream, Spl
 namespace {
 struct PaddedKey {
   uintptr_t ptr;
-  int64_t k, n;
+  int64_t k, n;  // n < 0: the entry holds the column sums of the [k, -n] weight
   bool operator<(const PaddedKey &o) const {
     return ptr != o.ptr ? ptr < o.ptr : k != o.k ? k < o.k : n < o.n;
   }
 };
-std::map<PaddedKey, __half *> g_padded_weights;  // guarded by g_const_mutex
+std::map<PaddedKey, void *> g_padded_weights;  // guarded by g_const_mutex
 }  // namespace
 
-const __half *padded_weight_lookup(const void *ptr, int64_t k, int64_t n) {
+namespace {
+void *derived_lookup(const void *ptr, int64_t k, int64_t n) {
   std::lock_guard<std::mutex> lock(g_const_mutex);
   auto it = g_padded_weights.find(PaddedKey{reinterpret_cast<uintptr_t>(ptr), k, n});
   return it == g_padded_weights.end() ? nullptr : it->second;
 }
-
-void padded_weight_insert(const void *ptr, int64_t k, int64_t n, __half *copy) {
+void derived_insert(const void *ptr, int64_t k, int64_t n, void *data) {
   std::lock_guard<std::mutex> lock(g_const_mutex);
-  __half *&slot = g_padded_weights[PaddedKey{reinterpret_cast<uintptr_t>(ptr), k, n}];
+  void *&slot = g_padded_weights[PaddedKey{reinterpret_cast<uintptr_t>(ptr), k, n}];
   if (slot) cudaFree(slot);
-  slot = copy;
+  slot = data;
 }
+}  // namespace
+
+const __half *padded_weight_lookup(const void *ptr, int64_t k, int64_t n) {
+  return static_cast<const __half *>(derived_lookup(ptr, k, n));
+}
+void padded_weight_insert(const void *ptr, int64_t k, int64_t n, __half *copy) { derived_insert(ptr, k, n, copy); }
+const float *weight_colsum_lookup(const void *ptr, int64_t k, int64_t n) {
+  return static_cast<const float *>(derived_lookup(ptr, k, -n));
+}
+void weight_colsum_insert(const void *ptr, int64_t k, int64_t n, float *sums) { derived_insert(ptr, k, -n, sums); }
 
 void declare_constant_range(const void *ptr, size_t bytes) {
   if (!ptr || bytes == 0) return;
@@ -185,7 +197,8 @@ void forget_constant_range(const void *ptr) {
   const uintptr_t e = range == g_const_ranges.end() ? b + 1 : range->second;
   if (range != g_const_ranges.end()) g_const_ranges.erase(range);
   // re-pitched copies of weights inside the withdrawn range go with it
-  for (auto it = g_padded_weights.lower_bound(PaddedKey{b, 0, 0}); it != g_padded_weights.end() && it->first.ptr < e;) {
+  for (auto it = g_padded_weights.lower_bound(PaddedKey{b, INT64_MIN, INT64_MIN});
+       it != g_padded_weights.end() && it->first.ptr < e;) {
     cudaFree(it->second);
     it = g_padded_weights.erase(it);
   }

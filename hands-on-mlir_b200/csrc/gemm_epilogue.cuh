@@ -28,6 +28,15 @@ struct EpilogueParams {
   const __half *row_scale;
   const __half *row_shift;
   const float *col_sum;
+  // Deferred LayerNorm (both null when unused).  `a_partials` / `r_partials` hold, per row, the
+  // sums and sums of squares of the raw A rows / raw residual rows per 64-column group
+  // ([groups][M] float2, what an earlier GEMM's `row_partials` wrote).  With a_partials the
+  // accumulator of the raw A is turned into LayerNorm(A).B (rstd * acc - mean * rstd * col_sum);
+  // with r_partials the residual added is LayerNorm(R) = rstd * R - mean * rstd instead of R.
+  const float2 *a_partials;
+  const float2 *r_partials;
+  int a_groups, r_groups;
+  float a_inv_n, r_inv_n, ln_eps;
   // 1 when N is not a multiple of 8: rows of C / D are then not 16-byte aligned, so C is read
   // element by element and D is written by the warp from its staging tile with 4- or 2-byte
   // stores instead of a TMA store.
@@ -104,6 +113,76 @@ constexpr uint32_t kEpilogueTileBytes = 32 * 128;
 constexpr uint32_t kEpilogueStageBytes = kEpilogueTileBytes;
 constexpr uint32_t kEpilogueStagingBytes = kEpilogueWarps * kEpilogueStageBytes;
 
+// Bits of the FORMS mask of the GEMM kernels and of epilogue_warp_block.
+constexpr int kFormLnA = 1, kFormLnR = 2, kFormStats = 4;
+
+// EPI: which of alpha, the C operand and the activation the instantiation handles.  The epilogue
+// is bound by instruction issue (every instruction per output element costs a tile about
+// elements / 128 cycles), so the three combinations a transformer layer is made of get
+// instantiations without the switches of the others; everything else takes the generic one.
+//   kEpiPlain  D = A.B                 (alpha 1, no C, no activation)
+//   kEpiGelu   D = gelu(A.B)           (alpha 1, no C)
+//   kEpiAddC   D = A.B + C             (alpha 1, beta 1, C a matrix or a row vector, no activation)
+constexpr int kEpiGeneric = 0, kEpiPlain = 1, kEpiGelu = 2, kEpiAddC = 3;
+
+// Per-row scalars of the LayerNorm forms of the epilogue: acc <- rs * acc + sh * col_sum[n]
+// (LayerNorm on A) and c <- rr * c + rt (LayerNorm on the residual); identity when unused.
+struct RowAffine {
+  float rs = 1.f, sh = 0.f, rr = 1.f, rt = 0.f;
+};
+
+__device__ __forceinline__ void row_stats_from_partials(const float2 *partials, int groups, int M, int row,
+                                                        float inv_n, float eps, float *rstd, float *shift) {
+  // Sixteen independent loads in flight at a time: the partial sums sit in L2 (the previous
+  // kernel wrote them), an L2 round trip under the operand stream takes a microsecond or more,
+  // and a dependent chain of them would outlast a short main loop.
+  float sum = 0.f, sq = 0.f;
+  const float2 *src = partials + row;
+  for (int g0 = 0; g0 < groups; g0 += 16) {
+    float2 v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      v[j] = g0 + j < groups ? __ldg(src + static_cast<long long>(g0 + j) * M) : make_float2(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      sum += v[j].x;
+      sq += v[j].y;
+    }
+  }
+  const float mean = sum * inv_n;
+  const float r = rsqrtf(fmaxf(fmaf(sq, inv_n, -mean * mean), 0.f) + eps);
+  *rstd = r;
+  *shift = -mean * r;
+}
+
+// Called before the accumulator wait so that the loads hide behind the main loop.
+__device__ __forceinline__ RowAffine epilogue_row_affine(const EpilogueParams &ep, int row) {
+  RowAffine ra;
+  if (row >= ep.M HOM_DIAG(|| (ep.dbg & 2048))) return ra;
+  if (ep.row_scale != nullptr) {
+    ra.rs = __half2float(ep.row_scale[row]);
+    ra.sh = __half2float(ep.row_shift[row]);
+  } else if (ep.a_partials != nullptr) {
+    row_stats_from_partials(ep.a_partials, ep.a_groups, ep.M, row, ep.a_inv_n, ep.ln_eps, &ra.rs, &ra.sh);
+  }
+  if (ep.r_partials != nullptr)
+    row_stats_from_partials(ep.r_partials, ep.r_groups, ep.M, row, ep.r_inv_n, ep.ln_eps, &ra.rr, &ra.rt);
+  return ra;
+}
+
+// The column sums of B for the 64 columns of a block, spread over the warp: lane l holds those
+// of columns c0 + l (x) and c0 + 32 + l (y), zeros beyond N.  The epilogue hands them round with
+// shuffles.  A CTA that works through several tiles requests the next tile's pair before it
+// starts on the current tile's epilogue: by then the next main loop is usually over, and the
+// round trip would be in the open.
+__device__ __forceinline__ float2 epilogue_load_col_sums(const EpilogueParams &ep, int c0, int lane) {
+  float2 cs = make_float2(0.f, 0.f);
+  if (ep.col_sum == nullptr HOM_DIAG(|| (ep.dbg & 4096))) return cs;
+  if (c0 + lane < ep.N) cs.x = __ldg(ep.col_sum + c0 + lane);
+  if (c0 + 32 + lane < ep.N) cs.y = __ldg(ep.col_sum + c0 + 32 + lane);
+  return cs;
+}
+
 // Requests the residual / bias values of one 64-column row segment (row `row`, columns
 // [c0, c0 + 64)), or of its 8-column groups [G0, G1) only; out-of-range groups come back as zeros.
 template <int G0 = 0, int G1 = 8>
@@ -151,12 +230,14 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
 // overwritten) while the store drains.  A warp whose column group lies outside the tile
 // (`active` false) only releases.
 // Returns false only when a split-K wait expired (the CTA's abort flag is then set).
-template <bool SPLIT = false, typename Release>
+template <bool SPLIT = false, int FORMS = 0, int EPI = 0, typename Release>
 __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, const CUtensorMap *tmD,
                                                     uint32_t tmem_addr, int row0, int c0, bool active,
                                                     uint32_t stage_smem, int lane, uint4 (&cval)[8],
                                                     Release release, const SplitK sk = SplitK(),
-                                                    volatile int *abort_flag = nullptr, int *status = nullptr) {
+                                                    volatile int *abort_flag = nullptr, int *status = nullptr,
+                                                    const RowAffine ra = RowAffine(),
+                                                    const float2 col_sums = float2{0.f, 0.f}) {
   using namespace hom::ptx;
   if (!active HOM_DIAG(|| (ep.dbg & 32))) {
     tc_fence_before_sync();
@@ -240,11 +321,17 @@ __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, co
   }
   const int row = row0 + lane;
   const uint32_t my_row = stage_smem + lane * 128;
-  float rs = 0.f, sh = 0.f;
-  if (ep.row_scale != nullptr && row < ep.M) {
-    rs = __half2float(ep.row_scale[row]);
-    sh = __half2float(ep.row_shift[row]);
-  }
+  // The LayerNorm forms exist only in the instantiations whose FORMS mask names them (kFormLnA:
+  // LayerNorm on A, kFormLnR: on the residual, kFormStats: statistics of D); inside such an
+  // instantiation each is still switched by its pointer.  The plain epilogue (FORMS 0) carries
+  // none of their code: the epilogue's instruction footprint is paid at every launch.
+  constexpr bool kLnA = (FORMS & kFormLnA) != 0, kLnR = (FORMS & kFormLnR) != 0, kStats = (FORMS & kFormStats) != 0;
+  const bool ln_on_a = kLnA && (ep.row_scale != nullptr || ep.a_partials != nullptr);
+  const bool ln_on_r = kLnR && ep.r_partials != nullptr;
+  const int valid_cols = ep.N - c0;  // columns of this block inside the matrix
+  const float2 rs2 = make_float2(ra.rs, ra.rs), sh2 = make_float2(ra.sh, ra.sh);
+  const float2 rr2 = make_float2(ra.rr, ra.rr);
+  float s1 = 0.f, s2 = 0.f;  // sum and sum of squares of this thread's 64 rounded outputs
   const float2 alpha2 = make_float2(ep.alpha, ep.alpha), beta2 = make_float2(ep.beta, ep.beta);
   const bool unit_alpha = ep.alpha == 1.0f;
 #pragma unroll
@@ -287,29 +374,53 @@ __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, co
       if (lane == 0) bulk_wait_group_read_0();
       __syncwarp();
     }
-    if (ep.row_scale != nullptr) {
+    if constexpr (kLnA) {
+      if (ln_on_a HOM_DIAG(&& !(ep.dbg & 1024))) {
+        // acc <- rstd * acc - mean * rstd * col_sum[column]; the shuffles are warp-uniform
+        const float mine = half == 0 ? col_sums.x : col_sums.y;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int col = c0 + half * 32 + i;
-        const float cs = col < ep.N ? ep.col_sum[col] : 0.f;
-        acc[i] = __float_as_uint(fmaf(rs, __uint_as_float(acc[i]), sh * cs));
+        for (int i = 0; i < 32; i += 2) {
+          const float2 cs = make_float2(__shfl_sync(0xffffffffu, mine, i), __shfl_sync(0xffffffffu, mine, i + 1));
+          const float2 a2 = make_float2(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]));
+          const float2 r = __ffma2_rn(rs2, a2, __fmul2_rn(sh2, cs));
+          acc[i] = __float_as_uint(r.x);
+          acc[i + 1] = __float_as_uint(r.y);
+        }
       }
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       const __half2 *h2 = reinterpret_cast<const __half2 *>(&cval[half * 4 + g]);
       uint32_t w[4];
+      // LayerNorm on the residual adds -mean * rstd: not beyond column N, where D stays zero
+      const float rt_1 = kLnR && half * 32 + g * 8 < valid_cols ? ra.rt : 0.f;
+      const float2 rt_g = make_float2(rt_1, rt_1);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int i0 = g * 8 + 2 * j;
         float2 v = make_float2(__uint_as_float(acc[i0]), __uint_as_float(acc[i0 + 1]));
         HOM_DIAG(if (!(ep.dbg & 2))) {
-          if (!unit_alpha) v = __fmul2_rn(alpha2, v);  // alpha * x is exact for alpha == 1: skip it
-          if (ep.c_mode != 0) v = __ffma2_rn(beta2, __half22float2(h2[j]), v);
-          if (ep.act == 1) v = gelu_erf_fast2(v);
+          if constexpr (EPI == kEpiGeneric) {
+            if (!unit_alpha) v = __fmul2_rn(alpha2, v);  // alpha * x is exact for alpha == 1: skip it
+          }
+          if (EPI == kEpiAddC || (EPI == kEpiGeneric && ep.c_mode != 0)) {
+            float2 c = __half22float2(h2[j]);
+            if constexpr (kLnR) {
+              if (ln_on_r) c = __ffma2_rn(rr2, c, rt_g);
+            }
+            v = EPI == kEpiAddC ? __fadd2_rn(c, v) : __ffma2_rn(beta2, c, v);
+          }
+          if (EPI == kEpiGelu || (EPI == kEpiGeneric && ep.act == 1)) v = gelu_erf_fast2(v);
         }
         const __half2 h = __floats2half2_rn(v.x, v.y);
         w[j] = *reinterpret_cast<const uint32_t *>(&h);
+        if constexpr (kStats) {
+          HOM_DIAG(if (ep.dbg & 256) continue;)
+          // statistics of what is stored: the rounded values (columns beyond N hold zeros)
+          const float2 q = __half22float2(h);
+          s1 += q.x + q.y;
+          s2 = fmaf(q.x, q.x, fmaf(q.y, q.y, s2));
+        }
       }
       const uint32_t addr = my_row + ((static_cast<uint32_t>(half * 4 + g) ^ (lane & 7u)) << 4);
 #if HOM_DIAG_ENABLED
@@ -323,26 +434,9 @@ __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, co
                    : "memory");
     }
   }
-  if (ep.row_partials != nullptr) {
-    // Each thread reads back the row it has just staged (its own writes: no barrier needed).
-    float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-    for (int chunk = 0; chunk < 8; ++chunk) {
-      uint32_t w[4];
-      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                   : "r"(my_row + ((static_cast<uint32_t>(chunk) ^ (lane & 7u)) << 4))
-                   : "memory");
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 q = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
-        const int col = c0 + chunk * 8 + 2 * j;
-        const float a = col < ep.N ? q.x : 0.f, b = col + 1 < ep.N ? q.y : 0.f;
-        s1 += a + b;
-        s2 = fmaf(a, a, fmaf(b, b, s2));
-      }
-    }
-    if (row < ep.M) ep.row_partials[static_cast<long long>(c0 >> 6) * ep.M + row] = make_float2(s1, s2);
+  if constexpr (kStats) {
+    if (ep.row_partials != nullptr && row < ep.M HOM_DIAG(&& !(ep.dbg & 512)))
+      ep.row_partials[static_cast<long long>(c0 >> 6) * ep.M + row] = make_float2(s1, s2);
   }
   if (!ep.unaligned_n) {
     fence_proxy_async_smem();

@@ -66,7 +66,7 @@ struct PairParams {
   HOM_DIAG(long long *tl;)    // optional launch-timeline slot, else null
 };
 
-template <int BN2, bool B_NK, bool SPLIT = false>
+template <int BN2, bool B_NK, bool SPLIT = false, int FORMS = 0, int EPI = 0>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const PairParams p) {
@@ -292,6 +292,11 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     int it = 0;
     HOM_DIAG(long long t_wait = 0; const long long t_begin = clock64();)
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
+    float2 next_col_sums = make_float2(0.f, 0.f);
+    if constexpr ((FORMS & kFormLnA) != 0) {
+      if (active && pair < p.num_units)
+        next_col_sums = epilogue_load_col_sums(p.ep, (pair % p.n_blocks) * BN2 + col_begin, lane);
+    }
     for (int unit = pair; unit < p.num_units; unit += num_pairs, ++it) {
       const int tile = unit / p.split_k;
       const int acc = it & 1;
@@ -308,7 +313,20 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         sk.slot = p.ws_slots + block * kSplitSlotFloats;
         sk.counter = p.ws_counters + block;
       } else {
-        if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cval);
+        if constexpr (EPI == kEpiGeneric || EPI == kEpiAddC) {
+          if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cval);
+        }
+      }
+      RowAffine ra;
+      float2 col_sums = make_float2(0.f, 0.f);
+      if constexpr ((FORMS & (kFormLnA | kFormLnR)) != 0) {
+        if (active) ra = epilogue_row_affine(p.ep, m0 + quarter * 32 + lane);
+      }
+      if constexpr ((FORMS & kFormLnA) != 0) {
+        col_sums = next_col_sums;
+        const int next = unit + num_pairs;
+        if (active && next < p.num_units)
+          next_col_sums = epilogue_load_col_sums(p.ep, (next % p.n_blocks) * BN2 + col_begin, lane);
       }
       HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
@@ -326,8 +344,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       };
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + col_begin;
-      if (!epilogue_warp_block<SPLIT>(p.ep, &tmD, t_row, m0 + quarter * 32, n0, active, stage_smem, lane, cval,
-                               release, sk, abort_flag, p.status))
+      if (!epilogue_warp_block<SPLIT, FORMS, EPI>(p.ep, &tmD, t_row, m0 + quarter * 32, n0, active, stage_smem, lane,
+                                             cval, release, sk, abort_flag, p.status, ra, col_sums))
         break;
     }
     // A store still in flight reads this warp's staging tile: let it finish reading.
@@ -358,8 +376,18 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  auto kernel = gemm_f16_pair_kernel<BN2, B_NK>;
+  // the whole-K kernel without LayerNorm forms: generic, or one of the three specialised epilogues
+  const int epi = epilogue_kind(pb);
+  auto kernel = epi == kEpiPlain  ? gemm_f16_pair_kernel<BN2, B_NK, false, 0, kEpiPlain>
+                : epi == kEpiGelu ? gemm_f16_pair_kernel<BN2, B_NK, false, 0, kEpiGelu>
+                : epi == kEpiAddC ? gemm_f16_pair_kernel<BN2, B_NK, false, 0, kEpiAddC>
+                                  : gemm_f16_pair_kernel<BN2, B_NK>;
   auto kernel_split = gemm_f16_pair_kernel<BN2, B_NK, true>;
+  // the LayerNorm forms of the epilogue: on A only / on the residual + statistics / any mix
+  const int forms = layernorm_forms(pb);
+  auto kernel_forms = forms == kFormLnA ? gemm_f16_pair_kernel<BN2, B_NK, false, kFormLnA>
+                      : (forms & kFormLnA) == 0 ? gemm_f16_pair_kernel<BN2, B_NK, false, kFormLnR | kFormStats>
+                                                : gemm_f16_pair_kernel<BN2, B_NK, false, kFormLnA | kFormLnR | kFormStats>;
 
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
@@ -376,9 +404,27 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   cfg.stream = stream;
 
   if (!attr_set[dev]) {
-    if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (!check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
                     "cudaFuncSetAttribute(gemm pair)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK, false, 0, kEpiPlain>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, plain)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK, false, 0, kEpiGelu>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, GELU)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK, false, 0, kEpiAddC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, + C)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK, false, kFormLnA>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, LayerNorm on A)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK, false, kFormLnR | kFormStats>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, LayerNorm on the residual)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_pair_kernel<BN2, B_NK, false, kFormLnA | kFormLnR | kFormStats>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm pair, LayerNorm forms)") ||
         !check_cuda(cudaFuncSetAttribute(kernel_split, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
                     "cudaFuncSetAttribute(gemm pair, split-K)"))
@@ -429,6 +475,13 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   p.ep.row_scale = pb.row_scale;
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
+  p.ep.a_partials = pb.a_partials;
+  p.ep.r_partials = pb.r_partials;
+  p.ep.a_groups = pb.a_groups;
+  p.ep.r_groups = pb.r_groups;
+  p.ep.a_inv_n = pb.K > 0 ? 1.f / static_cast<float>(pb.K) : 0.f;
+  p.ep.r_inv_n = pb.N > 0 ? 1.f / static_cast<float>(pb.N) : 0.f;
+  p.ep.ln_eps = pb.ln_eps;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
   p.ep.row_partials = pb.row_partials;
   HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
@@ -446,7 +499,7 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   })
   p.status = device_status_word();
   HOM_DIAG(p.prof = profile_buffer(); p.tl = launch_timeline_slot();)
-  p.split_k = split_k < 1 ? 1 : split_k > 16 ? 16 : split_k;
+  p.split_k = split_k < 1 || has_layernorm_form(pb) ? 1 : split_k > 16 ? 16 : split_k;
   if (p.split_k > p.num_kb) p.split_k = p.num_kb;
   p.num_units = p.num_tiles * p.split_k;
   p.ws_slots = nullptr;
@@ -465,7 +518,8 @@ bool launch_pair_variant(const Problem &pb, int split_k, cudaStream_t stream) {
                               static_cast<double>(pb.M) * pb.N) +
                        (pb.c_mode == 1 ? 2.0 * pb.M * pb.N : pb.c_mode == 2 ? 2.0 * pb.N : 0.0);
   LaunchScope scope(kOpGemm, flops, bytes);
-  if (!check_cuda(cudaLaunchKernelEx(&cfg, p.split_k > 1 ? kernel_split : kernel, tmA, tmB, tmD, p),
+  if (!check_cuda(cudaLaunchKernelEx(&cfg, forms != 0 ? kernel_forms : p.split_k > 1 ? kernel_split : kernel,
+                                     tmA, tmB, tmD, p),
                   "gemm pair kernel launch"))
     return false;
   HOM_DIAG(if (p.prof) profile_report("gemm CTA-pair", p.num_tiles, 2 * pairs, p.num_kb, stream);)

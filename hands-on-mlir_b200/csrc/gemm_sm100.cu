@@ -84,7 +84,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   }
 }
 
-template <int BN, bool B_NK, bool LN = false, bool SPLIT = false>
+template <int BN, bool B_NK, bool LN = false, bool SPLIT = false, int FORMS = 0, int EPI = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const Params p) {
@@ -299,6 +299,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     bool ln_done = false;
     HOM_DIAG(long long t_wait = 0; const long long t_begin = clock64();)
     pdl_wait();  // C may be produced, and D still read, by the previous kernel
+    float2 next_col_sums = make_float2(0.f, 0.f);
+    if constexpr ((FORMS & kFormLnA) != 0) {
+      if (active && static_cast<int>(blockIdx.x) < p.num_units)
+        next_col_sums = epilogue_load_col_sums(p.ep, (static_cast<int>(blockIdx.x) % p.n_blocks) * BN + col_begin, lane);
+    }
     for (int unit = blockIdx.x; unit < p.num_units; unit += gridDim.x, ++it) {
       const int tile = unit / p.split_k;
       const int acc = it & 1;
@@ -315,7 +320,20 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         sk.slot = p.ws_slots + block * kSplitSlotFloats;
         sk.counter = p.ws_counters + block;
       } else {
-        if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
+        if constexpr (EPI == kEpiGeneric || EPI == kEpiAddC) {
+          if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
+        }
+      }
+      RowAffine ra;
+      float2 col_sums = make_float2(0.f, 0.f);
+      if constexpr ((FORMS & (kFormLnA | kFormLnR)) != 0) {
+        if (active) ra = epilogue_row_affine(p.ep, m0 + quarter * 32 + lane);
+      }
+      if constexpr ((FORMS & kFormLnA) != 0) {
+        col_sums = next_col_sums;
+        const int next = unit + gridDim.x;
+        if (active && next < p.num_units)
+          next_col_sums = epilogue_load_col_sums(p.ep, (next % p.n_blocks) * BN + col_begin, lane);
       }
       HOM_DIAG(const long long tw = p.prof ? clock64() : 0;)
       bool ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kDevWaitTimeoutEpilogue);
@@ -338,10 +356,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                lane, cval, ln);
         ln_done = true;
       } else {
-        if (!epilogue_warp_block<SPLIT>(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active, stage_smem,
-                                 lane, cval, [&]() {
-                                   if (lane == 0) mbar_arrive(tempty_bar(acc));
-                                 }, sk, abort_flag, p.status))
+        if (!epilogue_warp_block<SPLIT, FORMS, EPI>(p.ep, &tmD, t_row, m0 + quarter * 32, n0 + col_begin, active,
+                                               stage_smem, lane, cval, [&]() {
+                                                 if (lane == 0) mbar_arrive(tempty_bar(acc));
+                                               }, sk, abort_flag, p.status, ra, col_sums))
           break;
       }
     }
@@ -579,12 +597,40 @@ bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kernel = gemm_f16_kernel<BN, B_NK>;
+  // the whole-K kernel without LayerNorm forms: generic, or one of the three specialised epilogues
+  const int epi = epilogue_kind(pb);
+  auto kernel = epi == kEpiPlain  ? gemm_f16_kernel<BN, B_NK, false, false, 0, kEpiPlain>
+                : epi == kEpiGelu ? gemm_f16_kernel<BN, B_NK, false, false, 0, kEpiGelu>
+                : epi == kEpiAddC ? gemm_f16_kernel<BN, B_NK, false, false, 0, kEpiAddC>
+                                  : gemm_f16_kernel<BN, B_NK>;
   auto kernel_split = gemm_f16_kernel<BN, B_NK, false, true>;
+  // the LayerNorm forms of the epilogue: on A only / on the residual + statistics / any mix
+  const int forms = layernorm_forms(pb);
+  auto kernel_forms = forms == kFormLnA ? gemm_f16_kernel<BN, B_NK, false, false, kFormLnA>
+                      : (forms & kFormLnA) == 0 ? gemm_f16_kernel<BN, B_NK, false, false, kFormLnR | kFormStats>
+                                                : gemm_f16_kernel<BN, B_NK, false, false, kFormLnA | kFormLnR | kFormStats>;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (!check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
                     "cudaFuncSetAttribute(gemm)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK, false, false, 0, kEpiPlain>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, plain)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK, false, false, 0, kEpiGelu>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, GELU)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK, false, false, 0, kEpiAddC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, + C)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK, false, false, kFormLnA>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, LayerNorm on A)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK, false, false, kFormLnR | kFormStats>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, LayerNorm on the residual)") ||
+        !check_cuda(cudaFuncSetAttribute(gemm_f16_kernel<BN, B_NK, false, false, kFormLnA | kFormLnR | kFormStats>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm, LayerNorm forms)") ||
         !check_cuda(cudaFuncSetAttribute(kernel_split, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
                     "cudaFuncSetAttribute(gemm, split-K)"))
@@ -623,6 +669,13 @@ bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   p.ep.row_scale = pb.row_scale;
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
+  p.ep.a_partials = pb.a_partials;
+  p.ep.r_partials = pb.r_partials;
+  p.ep.a_groups = pb.a_groups;
+  p.ep.r_groups = pb.r_groups;
+  p.ep.a_inv_n = pb.K > 0 ? 1.f / static_cast<float>(pb.K) : 0.f;
+  p.ep.r_inv_n = pb.N > 0 ? 1.f / static_cast<float>(pb.N) : 0.f;
+  p.ep.ln_eps = pb.ln_eps;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
   p.ep.row_partials = pb.row_partials;
   HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
@@ -637,7 +690,7 @@ bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
   })
   p.status = device_status_word();
   HOM_DIAG(p.prof = profile_buffer(); p.tl = launch_timeline_slot();)
-  p.split_k = clamp_split(split_k, p.num_kb);
+  p.split_k = has_layernorm_form(pb) ? 1 : clamp_split(split_k, p.num_kb);
   p.num_units = p.num_tiles * p.split_k;
   p.ws_slots = nullptr;
   p.ws_counters = nullptr;
@@ -654,8 +707,8 @@ bool launch_variant(const Problem &pb, int split_k, cudaStream_t stream) {
                               static_cast<double>(pb.M) * pb.N) +
                        (pb.c_mode == 1 ? 2.0 * pb.M * pb.N : pb.c_mode == 2 ? 2.0 * pb.N : 0.0);
   LaunchScope scope(kOpGemm, flops, bytes);
-  if (!check_cuda(launch_pdl(p.split_k > 1 ? kernel_split : kernel, dim3(grid), dim3(kThreads),
-                             Cfg::kSmemBytes, stream, 1, tmA, tmB, tmD, p),
+  if (!check_cuda(launch_pdl(forms != 0 ? kernel_forms : p.split_k > 1 ? kernel_split : kernel,
+                             dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, 1, tmA, tmB, tmD, p),
                   "gemm kernel launch"))
     return false;
   HOM_DIAG(if (p.prof) profile_report("gemm 1-CTA", p.num_tiles, grid, p.num_kb, stream);)
@@ -703,6 +756,10 @@ bool launch_ln_variant(const Problem &pb, float eps, cudaStream_t stream) {
   p.ep.row_scale = nullptr;
   p.ep.row_shift = nullptr;
   p.ep.col_sum = nullptr;
+  p.ep.a_partials = nullptr;
+  p.ep.r_partials = nullptr;
+  p.ep.a_groups = p.ep.r_groups = 0;
+  p.ep.a_inv_n = p.ep.r_inv_n = p.ep.ln_eps = 0.f;
   p.ep.unaligned_n = 0;
   p.ep.row_partials = nullptr;
   HOM_DIAG(p.ep.dbg = 0;)
@@ -793,7 +850,8 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
   constexpr int BN = 128;
   using Cfg = TileCfg<BN>;
   if (pb.M == 0 || pb.N == 0) return true;
-  auto kernel = gemm_f16_kernel<BN, false>;
+  // the instantiation with the LayerNorm forms of the epilogue: this path is the LayerNorm-on-A form
+  auto kernel = gemm_f16_kernel<BN, false, false, false, kFormLnA>;
   if (!check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::kSmemBytes),
                   "cudaFuncSetAttribute(gemm)"))
@@ -842,6 +900,13 @@ bool run_fixed_no_alloc(const Problem &pb, cudaStream_t stream) {
   p.ep.row_scale = pb.row_scale;
   p.ep.row_shift = pb.row_shift;
   p.ep.col_sum = pb.col_sum;
+  p.ep.a_partials = pb.a_partials;
+  p.ep.r_partials = pb.r_partials;
+  p.ep.a_groups = pb.a_groups;
+  p.ep.r_groups = pb.r_groups;
+  p.ep.a_inv_n = pb.K > 0 ? 1.f / static_cast<float>(pb.K) : 0.f;
+  p.ep.r_inv_n = pb.N > 0 ? 1.f / static_cast<float>(pb.N) : 0.f;
+  p.ep.ln_eps = pb.ln_eps;
   p.ep.unaligned_n = pb.N % 8 != 0 ? 1 : 0;
   p.ep.row_partials = pb.row_partials;
   HOM_DIAG(p.ep.dbg = std::getenv("HOM_EPI_DBG") ? std::atoi(std::getenv("HOM_EPI_DBG")) : 0;)
@@ -1197,7 +1262,7 @@ bool run(const Problem &pb, int tile_row, cudaStream_t stream) {
   } else {
     split = pb.split_k >= 2 ? pb.split_k : 1;
   }
-  if (pb.row_partials) split = 1;  // the statistics come from the finished tile's epilogue
+  if (has_layernorm_form(pb)) split = 1;  // those epilogue forms exist for whole-K tiles only
   const TileRow &t = kTileRows[tile_row];
   if (t.pair) return run_pair(pb, t.tile_n, split, stream);
   if (pb.b_is_nk) {

@@ -33,10 +33,33 @@ struct Problem {
   const __half *row_scale = nullptr;
   const __half *row_shift = nullptr;
   const float *col_sum = nullptr;
+  // Deferred LayerNorm (see EpilogueParams): fp32 per-row partial sums of the raw A ([a_groups][M]
+  // float2, needs col_sum) and / or of the raw residual ([r_groups][M] float2).
+  const float2 *a_partials = nullptr;
+  const float2 *r_partials = nullptr;
+  int a_groups = 0, r_groups = 0;
+  float ln_eps = 0.f;
   // When set: the epilogue also leaves per-row, per-64-column-group sums and sums of squares of
   // D here ([ceil(N / 64)][M] float2), see EpilogueParams::row_partials.  Forces split_k = 1.
   float2 *row_partials = nullptr;
 };
+
+// Which LayerNorm forms the epilogue applies (bits: 1 LayerNorm on A, 2 LayerNorm on the
+// residual, 4 statistics of D; the kForm* constants of gemm_epilogue.cuh).  Those forms live in
+// their own kernel instantiations and need whole-K tiles (no split-K).
+inline int layernorm_forms(const Problem &pb) {
+  return ((pb.row_scale != nullptr || pb.a_partials != nullptr) ? 1 : 0) | (pb.r_partials != nullptr ? 2 : 0) |
+         (pb.row_partials != nullptr ? 4 : 0);
+}
+inline bool has_layernorm_form(const Problem &pb) { return layernorm_forms(pb) != 0; }
+
+// Which specialised epilogue fits `pb` (the kEpi* constants of gemm_epilogue.cuh): 1 D = A.B,
+// 2 D = gelu(A.B), 3 D = A.B + C, each with alpha = 1 (and beta = 1); 0 the generic one.
+inline int epilogue_kind(const Problem &pb) {
+  if (pb.alpha != 1.0f || pb.N % 8 != 0) return 0;
+  if (pb.c_mode == 0) return pb.act == 0 ? 1 : pb.act == 1 ? 2 : 0;
+  return pb.beta == 1.0f && pb.act == 0 ? 3 : 0;
+}
 
 // Enqueues the GEMM; tile_row 1..4 forces one CTA per 128 x {64,128,192,256} tile, 5..6 one
 // CTA pair per 256 x {128,256} tile; anything else lets the tile table / heuristic decide.

@@ -84,6 +84,10 @@ bool is_constant_range(const void *ptr, size_t bytes);
 // when there is none yet; insert takes ownership of a cudaMalloc'ed copy.
 const __half *padded_weight_lookup(const void *ptr, int64_t k, int64_t n);
 void padded_weight_insert(const void *ptr, int64_t k, int64_t n, __half *copy);
+// The same store for the fp32 column sums of a declared weight (N floats; the LayerNorm-on-A
+// forms of the GEMM epilogue need them): computed once, dropped with the declaration.
+const float *weight_colsum_lookup(const void *ptr, int64_t k, int64_t n);
+void weight_colsum_insert(const void *ptr, int64_t k, int64_t n, float *sums);
 // Programmatic dependent launch is on unless HOM_DISABLE_PDL is set (diagnostics).
 bool pdl_enabled();
 // Host-mapped status word that device code writes on a bounded-wait expiry (device pointer).

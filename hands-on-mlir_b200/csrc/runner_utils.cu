@@ -754,6 +754,99 @@ void homGemmResidualLayernormF16(int64_t rankA, void *dstA, int64_t rankB, void 
   hom::gemm::run_layernorm_fused(pb, eps, hom::current_stream());
 }
 
+// fp32 partial row sums [groups, rows, 2]; absent (rank 0 / null) gives *out = null.
+bool partials_operand(const char *name, const char *what, int64_t rank, void *dst, int64_t groups,
+                      int64_t rows, float2 **out) {
+  *out = nullptr;
+  if (dst == nullptr || rank == 0) return true;
+  MemRefView v = view_memref(rank, dst, 4);
+  if (!v.valid || v.rank != 3 || v.sizes[0] != groups || v.sizes[1] != rows || v.sizes[2] != 2 ||
+      !v.contiguous() || (reinterpret_cast<uintptr_t>(v.ptr) & 7u) != 0) {
+    set_error(HOM_ERR_INVALID, "%s: %s must be a contiguous fp32 memref of shape [%lld, %lld, 2]", name, what,
+              static_cast<long long>(groups), static_cast<long long>(rows));
+    return false;
+  }
+  *out = reinterpret_cast<float2 *>(v.ptr);
+  return true;
+}
+
+void homGemmDeferredLayernormF16(int64_t rankA, void *dstA, int64_t rankStatsA, void *dstStatsA,
+                                 int64_t rankB, void *dstB, bool weightsNK, int64_t rankR, void *dstR,
+                                 int64_t rankStatsR, void *dstStatsR, int64_t rankD, void *dstD,
+                                 int64_t rankStatsD, void *dstStatsD, int64_t activation, float eps) {
+  const char *name = "homGemmDeferredLayernormF16";
+  hom::gemm::Problem pb;
+  bool empty = false;
+  const bool has_r = dstR != nullptr && rankR > 0;
+  if (!gemm_prepare(name, weightsNK, rankA, dstA, rankB, dstB, rankR, dstR, rankD, dstD, activation, 1.f,
+                    has_r ? 1.f : 0.f, &pb, &empty))
+    return;
+  if (pb.c_mode == 2 || pb.N % 8 != 0) {
+    set_error(HOM_ERR_UNSUPPORTED, "%s: the residual must have the shape of the output and N % 8 == 0", name);
+    return;
+  }
+  float2 *stats_a = nullptr, *stats_r = nullptr, *stats_d = nullptr;
+  const int64_t ga = (pb.K + 63) / 64, gd = (pb.N + 63) / 64;
+  if (!partials_operand(name, "the statistics of A", rankStatsA, dstStatsA, ga, pb.M, &stats_a) ||
+      !partials_operand(name, "the statistics of R", rankStatsR, dstStatsR, gd, pb.M, &stats_r) ||
+      !partials_operand(name, "the statistics of D", rankStatsD, dstStatsD, gd, pb.M, &stats_d))
+    return;
+  if (stats_r && !has_r) {
+    set_error(HOM_ERR_INVALID, "%s: statistics of R given without R", name);
+    return;
+  }
+  if (stats_d && (stats_d == stats_r || stats_d == stats_a)) {
+    set_error(HOM_ERR_INVALID,
+              "%s: the statistics of D must not overwrite those of A or R (other tiles still read them)", name);
+    return;
+  }
+  cudaStream_t stream = hom::current_stream();
+  if (stats_a) {
+    // LayerNorm(A).B = rstd * (A.B) - mean * rstd * colsum(B): the column sums of a declared
+    // weight are computed once and kept, those of any other B on every call.
+    const float *sums = pb.b_const ? hom::weight_colsum_lookup(pb.B, pb.K, pb.N) : nullptr;
+    if (!sums) {
+      float *fresh = nullptr;
+      if (pb.b_const) {
+        void *ptr = nullptr;
+        if (!hom::check_cuda(cudaMalloc(&ptr, static_cast<size_t>(pb.N) * sizeof(float)), "cudaMalloc(column sums)"))
+          return;
+        fresh = static_cast<float *>(ptr);
+      } else {
+        if (pb.N > kColSumCapacity) {
+          set_error(HOM_ERR_UNSUPPORTED, "%s: N = %lld exceeds the %lld-column scratch", name,
+                    static_cast<long long>(pb.N), static_cast<long long>(kColSumCapacity));
+          return;
+        }
+        fresh = col_sum_scratch();
+        if (!fresh) return;
+      }
+      if (!hom::bw::col_sum_f16(pb.B, fresh, pb.K, pb.N, weightsNK, stream)) {
+        if (pb.b_const) cudaFree(fresh);
+        return;
+      }
+      if (pb.b_const) {
+        if (!hom::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize(column sums)")) {
+          cudaFree(fresh);
+          return;
+        }
+        hom::weight_colsum_insert(pb.B, pb.K, pb.N, fresh);
+      }
+      sums = fresh;
+    }
+    pb.col_sum = sums;
+    pb.a_partials = stats_a;
+    pb.a_groups = static_cast<int>(ga);
+  }
+  if (stats_r) {
+    pb.r_partials = stats_r;
+    pb.r_groups = static_cast<int>(gd);
+  }
+  pb.row_partials = stats_d;
+  pb.ln_eps = eps;
+  hom::gemm::run(pb, 0, stream);
+}
+
 void homBertEmbeddingF16(int64_t rankIds, void *dstIds, int64_t rankTypes, void *dstTypes,
                          int64_t rankWord, void *dstWord, int64_t rankPos, void *dstPos,
                          int64_t rankTypeEmb, void *dstTypeEmb, int64_t rankOut, void *dstOut,

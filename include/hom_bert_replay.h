@@ -42,8 +42,13 @@ typedef struct HomBertConfig {
   int32_t weights_nk;  /* 0: weights [1,K,N] via cutlassGemmF16; 1: [1,N,K] via nvteGemmF16 */
   int32_t fused_embedding; /* 1: homBertEmbeddingF16 in place of the five embedding calls
                               (same bits; not what the reference's lowering emits) */
-  int32_t fused_layernorm; /* 1: homGemmResidualLayernormF16 in place of the GEMM + LayerNorm call
-                              pairs (out-projection, FFN2); same values within the op tolerance */
+  int32_t fused_layernorm; /* 0: the reference's call sequence (GEMM, then nvteLayernormF16);
+                              1: homGemmResidualLayernormF16 in place of the GEMM + LayerNorm call
+                              pairs (out-projection, FFN2); same values within the op tolerance;
+                              2: deferred LayerNorm (homGemmDeferredLayernormF16): the residual
+                              stream stays raw with fp32 row statistics and every GEMM applies
+                              the LayerNorm of its operands in its epilogue - no LayerNorm launch
+                              inside the layers, one after the last */
 } HomBertConfig;
 
 /* Number of weight tensors a program with this config takes: 3 embeddings + 4 per layer.

@@ -226,6 +226,27 @@ HOM_EXPORT void homBertEmbeddingF16(int64_t rankIds, void *dstIds, int64_t rankT
                                     int64_t rankTypeEmb, void *dstTypeEmb, int64_t rankOut,
                                     void *dstOut, float eps);
 
+/* GEMM with the LayerNorms around it deferred into its epilogue, so that a post-LayerNorm
+ * transformer layer needs no LayerNorm launch at all:
+ *   D = act( LN?(A).B + LN?(R) ),  and optionally the row statistics of D for the next call.
+ * Every tensor that is "raw" (not yet normalised) travels with fp32 partial sums of its rows,
+ * shape [ceil(width / 64), rows, 2] = {sum, sum of squares} per 64-column group, exactly what a
+ * previous call wrote through StatsD.  StatsA given: A is raw and the epilogue computes
+ * LN(A).B as rstd * (A.B) - mean * rstd * colsum(B) (column sums of a declared weight are kept).
+ * StatsR given: the residual added is LN(R) = rstd * R - mean * rstd (R raw; R may alias D).
+ * StatsD given: the epilogue writes D's partial sums (of the fp16-rounded values) there.  Absent
+ * operands are rank-0 / null descriptors.  LayerNorm is the reference's (no affine, biased
+ * variance, eps inside the square root); statistics stay in fp32 - the sm_100a form of the
+ * reference's experimental cutlassGemmWithVarMeanF16 / cutlassLayernormGemmF16 pair
+ * (include/NVGPUKernels/LayernormGemmRunner.h:17-361), which stores them in fp16 and cannot
+ * express BERT's normalised residual.  A [.., M, K], B [1, K, N] or [1, N, K] (weightsNK),
+ * R, D [.., M, N], N % 8 == 0; activation 0 or 1 (erf GELU). */
+HOM_EXPORT void homGemmDeferredLayernormF16(int64_t rankA, void *dstA, int64_t rankStatsA, void *dstStatsA,
+                                            int64_t rankB, void *dstB, bool weightsNK, int64_t rankR,
+                                            void *dstR, int64_t rankStatsR, void *dstStatsR, int64_t rankD,
+                                            void *dstD, int64_t rankStatsD, void *dstStatsD,
+                                            int64_t activation, float eps);
+
 /* Out = LayerNorm(X + R) * gamma + beta over the last dimension; X, R, Out [rows.., H]
  * fp16 (R, gamma, beta may be rank-0 descriptors = absent), fp32 sum and statistics,
  * one fp16 rounding at the store.  Out may alias X. */
