@@ -877,6 +877,9 @@ def run_gpu_arm(args, cfg, workload):
             "gpu_launches_per_step": m["launches_per_forward"],
             "roofline": m["roofline"],
             "kernels": m["kernels"],
+            "kernels_note": ("per-launch CUDA events serialise the launches; the floor of this measurement is "
+                             f"{1e3 * m['kernels'].get('cu_seqlen', {}).get('serialised_ms_per_step', 0.0):.1f} us, what the "
+                             "one-block cu_seqlen kernel takes in it: compare shares, not absolutes"),
             "gemm_by_shape": m["gemm_by_shape"],
             "extensions": m.get("extensions"),
             "clocks": m["clocks"],

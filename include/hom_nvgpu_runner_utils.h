@@ -240,7 +240,11 @@ HOM_EXPORT void homBertEmbeddingF16(int64_t rankIds, void *dstIds, int64_t rankT
  * reference's experimental cutlassGemmWithVarMeanF16 / cutlassLayernormGemmF16 pair
  * (include/NVGPUKernels/LayernormGemmRunner.h:17-361), which stores them in fp16 and cannot
  * express BERT's normalised residual.  A [.., M, K], B [1, K, N] or [1, N, K] (weightsNK),
- * R, D [.., M, N], N % 8 == 0; activation 0 or 1 (erf GELU). */
+ * R, D [.., M, N], N % 8 == 0; activation 0 or 1 (erf GELU).  StatsD must not be the buffer
+ * of StatsA or StatsR (other tiles still read them).  With StatsA, the first call for a declared
+ * weight computes and caches its column sums (allocates device memory and waits for the stream):
+ * make that call outside of any stream capture; for any other B the sums are recomputed by an
+ * extra launch on every call (N <= 65536). */
 HOM_EXPORT void homGemmDeferredLayernormF16(int64_t rankA, void *dstA, int64_t rankStatsA, void *dstStatsA,
                                             int64_t rankB, void *dstB, bool weightsNK, int64_t rankR,
                                             void *dstR, int64_t rankStatsR, void *dstStatsR, int64_t rankD,
