@@ -171,7 +171,7 @@ class ClockSampler:
     def __exit__(self, *exc):
         self._stop.set()
         if self._thread:
-            self._thread.join()
+            self._thread.join(timeout=2.0)  # a stuck NVML query must not hold up the benchmark
 
     def summary(self):
         if not self.samples:

@@ -185,7 +185,7 @@ __device__ __forceinline__ float2 epilogue_load_col_sums(const EpilogueParams &e
 
 // Requests the residual / bias values of one 64-column row segment (row `row`, columns
 // [c0, c0 + 64)), or of its 8-column groups [G0, G1) only; out-of-range groups come back as zeros.
-template <int G0 = 0, int G1 = 8>
+template <int G0 = 0, int G1 = 8, bool ALIGNED_ONLY = false>
 __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int row, int c0, uint4 (&cval)[8]) {
   if (ep.c_mode == 0) return;
   HOM_DIAG(if (ep.dbg & 48) {
@@ -194,7 +194,7 @@ __device__ __forceinline__ void epilogue_load_c(const EpilogueParams &ep, int ro
   })
   const __half *cp = ep.c_mode == 1 ? ep.C + static_cast<long long>(row) * ep.ldc + c0 : ep.C + c0;
   const bool row_ok = ep.c_mode == 2 || row < ep.M;
-  if (ep.unaligned_n) {
+  if (!ALIGNED_ONLY && ep.unaligned_n) {
     // element-wise reads, packed in registers (no addressable array: keeps cval out of local memory)
     const unsigned short *cu = reinterpret_cast<const unsigned short *>(cp);
 #pragma unroll
@@ -334,8 +334,9 @@ __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, co
   float s1 = 0.f, s2 = 0.f;  // sum and sum of squares of this thread's 64 rounded outputs
   const float2 alpha2 = make_float2(ep.alpha, ep.alpha), beta2 = make_float2(ep.beta, ep.beta);
   const bool unit_alpha = ep.alpha == 1.0f;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  // One 32-column half of the block (both halves unrolled: the second half's accumulator read
+  // overlaps the first half's arithmetic).
+  auto do_half = [&](const int half) {
     uint32_t acc[32];
 #if HOM_DIAG_ENABLED
     if (ep.dbg & 1) {
@@ -433,12 +434,15 @@ __device__ __forceinline__ bool epilogue_warp_block(const EpilogueParams &ep, co
                    "r"(w[2]), "r"(w[3])
                    : "memory");
     }
-  }
+    };
+  do_half(0);
+  do_half(1);
   if constexpr (kStats) {
     if (ep.row_partials != nullptr && row < ep.M HOM_DIAG(&& !(ep.dbg & 512)))
       ep.row_partials[static_cast<long long>(c0 >> 6) * ep.M + row] = make_float2(s1, s2);
   }
-  if (!ep.unaligned_n) {
+  // (the specialised epilogues and the LayerNorm forms are only chosen when N % 8 == 0)
+  if ((EPI != kEpiGeneric || FORMS != 0) || !ep.unaligned_n) {
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {

@@ -314,7 +314,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         sk.counter = p.ws_counters + block;
       } else {
         if constexpr (EPI == kEpiGeneric || EPI == kEpiAddC) {
-          if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0, cval);
+          if (active) epilogue_load_c<0, 8, EPI != kEpiGeneric || FORMS != 0>(p.ep, m0 + quarter * 32 + lane, n0, cval);
         }
       }
       RowAffine ra;

@@ -321,7 +321,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         sk.counter = p.ws_counters + block;
       } else {
         if constexpr (EPI == kEpiGeneric || EPI == kEpiAddC) {
-          if (active) epilogue_load_c(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
+          if (active) epilogue_load_c<0, 8, EPI != kEpiGeneric || FORMS != 0>(p.ep, m0 + quarter * 32 + lane, n0 + col_begin, cval);
         }
       }
       RowAffine ra;
@@ -1262,7 +1262,14 @@ bool run(const Problem &pb, int tile_row, cudaStream_t stream) {
   } else {
     split = pb.split_k >= 2 ? pb.split_k : 1;
   }
-  if (has_layernorm_form(pb)) split = 1;  // those epilogue forms exist for whole-K tiles only
+  if (has_layernorm_form(pb)) {
+    split = 1;  // those epilogue forms exist for whole-K tiles only
+    if (pb.N % 8 != 0) {
+      set_error(HOM_ERR_UNSUPPORTED, "the LayerNorm forms of the GEMM epilogue need N %% 8 == 0 (got N = %lld)",
+                static_cast<long long>(pb.N));
+      return false;
+    }
+  }
   const TileRow &t = kTileRows[tile_row];
   if (t.pair) return run_pair(pb, t.tile_n, split, stream);
   if (pb.b_is_nk) {
