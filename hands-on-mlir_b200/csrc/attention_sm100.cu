@@ -394,6 +394,7 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   const uint32_t smem_p = smem_base;  // two 128 x 64 sub-tiles over Q|K
   const uint32_t bar_load = smem_base + 3 * kTileBytes;
   const uint32_t bar_s = bar_load + 8, bar_o = bar_load + 16;
+  const uint32_t bar_v = bar_load + 32;  // V arrives on its own barrier: S and the softmax do not wait for it
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + 3 * kTileBytes + 24);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   float *xchg_max = reinterpret_cast<float *>(smem_gen + 3 * kTileBytes + 64);  // [2][128]
@@ -401,6 +402,7 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
 
   if (tid == 0) {
     mbar_init(bar_load, 1);
+    mbar_init(bar_v, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
@@ -429,10 +431,11 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
   const bool leader = warp == 0 && elect_one();
   if (leader) {
     const int row_base = batch * p.seq;
-    mbar_arrive_expect_tx(bar_load, 3 * kTileBytes);
+    mbar_arrive_expect_tx(bar_load, 2 * kTileBytes);
     tma_load_2d(smem_q, &tmQKV, bar_load, head * kHeadDim, row_base);
     tma_load_2d(smem_k, &tmQKV, bar_load, hidden + head * kHeadDim, row_base);
-    tma_load_2d(smem_v, &tmQKV, bar_load, 2 * hidden + head * kHeadDim, row_base);
+    mbar_arrive_expect_tx(bar_v, kTileBytes);
+    tma_load_2d(smem_v, &tmQKV, bar_v, 2 * hidden + head * kHeadDim, row_base);
   }
   int len = p.cu_seqlens[batch + 1] - p.cu_seqlens[batch];
   len = max(0, min(len, p.seq));
@@ -537,7 +540,8 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
       stamp(6);
       const float l_row = l_part + xchg_sum[(hf ^ 1) * kTile + row];
       inv = (row_live && l_row > 0.f) ? 1.f / l_row : 0.f;
-      if (warp == 0) {
+      if (warp == 0 &&
+          __all_sync(0xffffffffu, mbar_wait(bar_v, 0, abort_flag, p.status, kDevWaitTimeoutAttention))) {
         tc_fence_after_sync();
         constexpr uint32_t idesc_o = make_idesc_f16(kTile, kHeadDim, false, true);
         const int k_steps = (len + 15) >> 4;  // key groups beyond the last valid key hold no P
@@ -559,6 +563,7 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
     // Nothing was computed, but the tile copies are in flight: they must land before the
     // zero tile is staged over V (and before shared memory is released).
     ok = mbar_wait(bar_load, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
+    ok = ok && mbar_wait(bar_v, 0, abort_flag, p.status, kDevWaitTimeoutAttention);
     ok = __syncthreads_and(ok);
   }
   if (ok) {
@@ -609,6 +614,8 @@ attention_f16_single_tile_kernel(const __grid_constant__ CUtensorMap tmQKV,
     // Let copies that are still in flight land before the shared memory is released.
     const long long t0 = clock64();
     while (!mbar_try_wait(bar_load, 0) && clock64() - t0 < 200000000LL) {
+    }
+    while (!mbar_try_wait(bar_v, 0) && clock64() - t0 < 400000000LL) {
     }
   }
 
