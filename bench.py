@@ -770,9 +770,14 @@ def torch_cpu_baseline(cfg, workload, budget_s: float = 10.0):
 
 
 def run_gpu_arm(args, cfg, workload):
+    import faulthandler
     import torch
     import torch.distributed as dist
     from __graft_entry__ import load_package
+
+    # A GPU arm that makes no progress must not sit in a synchronize call for ever: after 20
+    # minutes the Python stacks are dumped to stderr and the process exits non-zero.
+    faulthandler.dump_traceback_later(1200, exit=True)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

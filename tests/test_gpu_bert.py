@@ -258,6 +258,7 @@ def test_batch_composition_does_not_change_a_sequence(hom, cuda, oracle):
         # elements differ by more than rtol/atol 1e-3 after three layers, 4e-6 by more than 2e-3;
         # both runs are equally close to the oracle).
         f1, f2, fref = drift_fractions(alone[0, :lens[b]], full[b, :lens[b]])
+        print(f"sequence {b}: alone vs in the batch of 6: {f1:.2e} of the elements outside 1e-3, {f2:.2e} outside 2e-3")
         assert f1 <= 5e-3 and f2 <= 1e-4 and fref == 0.0, (b, f1, f2, fref)
 
 
