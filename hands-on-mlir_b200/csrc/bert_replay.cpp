@@ -18,6 +18,7 @@ struct Tensor {
   void *desc = nullptr;  // {basePtr, data, offset, sizes[rank], strides[rank]}
   bool owned_buffer = false;
   bool owned_desc = false;
+  const void *declared = nullptr;  // start of the constant range this program declared for it
 
   void *data() const { return desc ? static_cast<void **>(desc)[1] : nullptr; }
 };
@@ -77,6 +78,9 @@ struct Program {
 
 void release(Tensor &t, bool f16) {
   if (t.desc) {
+    // A caller-owned weight stops being a declared constant with the program: the caller may
+    // free or rewrite it afterwards.
+    if (t.declared) homForgetWeights(t.declared);
     if (t.owned_buffer) {
       if (f16) deallocNVGPUF16(t.rank, t.desc);
       else deallocNVGPUI32(t.rank, t.desc);
@@ -356,7 +360,9 @@ int homBertSetWeight(void *program, int32_t index, int64_t rank, void *descripto
     const int64_t *w = static_cast<const int64_t *>(copy);
     int64_t n = 1;
     for (int64_t i = 0; i < rank; ++i) n *= w[3 + i];
-    homDeclareWeights(reinterpret_cast<const char *>(static_cast<void *const *>(copy)[1]) + 2 * w[2], 2 * n);
+    const char *first = reinterpret_cast<const char *>(static_cast<void *const *>(copy)[1]) + 2 * w[2];
+    homDeclareWeights(first, 2 * n);
+    p->weights[index].declared = first;
   }
   if (p->graph_exec) {
     cudaGraphExecDestroy(p->graph_exec);

@@ -187,6 +187,13 @@ void declare_constant_range(const void *ptr, size_t bytes) {
   if (!ptr || bytes == 0) return;
   const uintptr_t b = reinterpret_cast<uintptr_t>(ptr);
   std::lock_guard<std::mutex> lock(g_const_mutex);
+  // A (re)declaration says "constant from now on": whatever was derived from an earlier content
+  // of these addresses (re-pitched copies, column sums) is stale.
+  for (auto it = g_padded_weights.lower_bound(PaddedKey{b, INT64_MIN, INT64_MIN});
+       it != g_padded_weights.end() && it->first.ptr < b + bytes;) {
+    cudaFree(it->second);
+    it = g_padded_weights.erase(it);
+  }
   g_const_ranges[b] = b + bytes;
 }
 

@@ -188,8 +188,11 @@ HOM_EXPORT int homSynchronize(void);
  * that an earlier call on the stream produced is always read after it was written.  Buffers
  * returned by allocConstantNVGPU* are declared by the library; callers that bring their own
  * weight buffers may declare them to get the earlier prefetch.  homForgetWeights() withdraws a
- * declaration (call it before the buffer is freed or reused).  No counterpart in the reference,
- * whose launches are fully serialised on the null stream. */
+ * declaration (call it before the buffer is freed or reused).  What the library derives from a
+ * declared weight and keeps (a re-pitched copy for N % 8 != 0, column sums for the deferred
+ * LayerNorm) is dropped when the weight is forgotten and when it is declared again: declare a
+ * buffer again after rewriting its contents.  No counterpart in the reference, whose launches
+ * are fully serialised on the null stream. */
 HOM_EXPORT void homDeclareWeights(const void *ptr, int64_t bytes);
 HOM_EXPORT void homForgetWeights(const void *ptr);
 

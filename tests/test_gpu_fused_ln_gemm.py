@@ -235,6 +235,30 @@ def test_deferred_layernorm_on_the_residual_and_statistics_out(hom, cuda, oracle
     np.testing.assert_allclose(stats_out.cpu().numpy(), _partials(got), rtol=2e-5, atol=2e-4)
 
 
+def test_column_sums_of_a_declared_weight_follow_a_new_declaration(hom, cuda, oracle):
+    """The column sums kept for a declared weight are dropped when the same buffer is declared
+    again with new contents (and when it is forgotten)."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(77))
+    m, n, k = 256, 256, 320
+    A = f16(rng.normal(0.5, 1.0, (1, m, k)))
+    tA, tS = to_dev(A, cuda), to_dev(_partials(A[0]), cuda)
+    tB = torch.empty((1, k, n), dtype=torch.float16, device=cuda)
+    D = torch.empty((1, m, n), dtype=torch.float16, device=cuda)
+    for round_ in range(3):
+        B = f16(rng.normal(0.01 * round_, 0.03, (1, k, n)))
+        if round_ == 2:
+            hom.forget_weights(tB)
+        tB.copy_(torch.from_numpy(B))
+        hom.declare_weights(tB)
+        for _ in range(2):  # the second call uses the kept sums
+            hom.homGemmDeferredLayernormF16(tA, tS, tB, None, None, D, None, eps=1e-12)
+        hom.synchronize()
+        want = _ln64(A[0], 1e-12) @ B[0].astype(np.float64)
+        assert_close_f16(D.cpu().numpy()[0], want, f"declaration {round_}", rtol=1.5e-3, atol=1.5e-3)
+    hom.forget_weights(tB)
+
+
 def test_deferred_layernorm_rejects_bad_statistics(hom, cuda, pkg):
     import torch
     A = torch.zeros((1, 128, 128), dtype=torch.float16, device=cuda)
