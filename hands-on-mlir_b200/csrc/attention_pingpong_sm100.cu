@@ -384,6 +384,16 @@ attention_f16_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const P
         // scale > 0, so the maximum of the scaled scores is the scaled maximum
         const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
         const float corr = ex2_fast(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+        // The tile's P buffer still holds the previous step's probabilities until that step's
+        // P.V product has read them.  Its MMAs were queued right after this step's S, so they are
+        // normally long done (the fold below waits for the same phase), but nothing else orders
+        // them before the stores of pass 2: a short pass 1 (a ragged last KV tile with a few
+        // valid keys) can get here first.
+        if (j > 0) {
+          ok = mbar_wait(o_full(t, o_uses & 1u), (o_uses >> 1) & 1u, abort_flag, p.status, kDevWaitTimeoutAttention);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
         // ---- pass 2: P = exp2(scale * S - m) as fp16 into shared memory, row sum in fp32
         float2 l2 = make_float2(0.f, 0.f);
         const float2 neg_m2 = make_float2(-m_new, -m_new);

@@ -587,3 +587,29 @@ def test_constant_loader_binary_cache(hom, cuda, oracle, tmp_path):
         assert_bits_equal(load(), want2, "constant, cache invalidated")
     finally:
         hom.lib.homSetConstantCache(0)
+
+
+def test_two_query_tile_attention_repeats_bit_for_bit_with_a_one_key_last_tile(hom, cuda, oracle):
+    """Sequence lengths one past a multiple of 128 give the last KV step a single valid key and
+    its softmax a very short first pass: the step's probabilities must still not be stored
+    before the previous step's P.V product has read the buffer.  Checked against the oracle
+    once and bit for bit over repeats."""
+    import torch
+    B, S, H = 6, 512, 16
+    lens = np.array([257, 129, 385, 257, 300, 130])
+    rng = np.random.Generator(np.random.PCG64(91))
+    qkv = rng.normal(0, 1, (B, S, 3 * H * 64)).astype(np.float32).astype(np.float16)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    tq, tc = to_dev(qkv, cuda), to_dev(cu, cuda)
+    out = torch.empty((B, S, H * 64), dtype=torch.float16, device=cuda)
+    hom.nvteBertAttentionF16(tq, tc, out, 0.125, H)
+    hom.synchronize()
+    first = out.clone()
+    want = oracle.attention_f16(qkv, cu, H, 0.125)
+    for b, n in enumerate(lens):
+        assert_close_f16(first[b, :n].cpu().numpy(), want[b, :n], f"sequence {b} (length {n})")
+    for _ in range(100):
+        out.zero_()
+        hom.nvteBertAttentionF16(tq, tc, out, 0.125, H)
+        assert torch.equal(out, first)
+    hom.synchronize()
