@@ -142,7 +142,7 @@ __device__ __forceinline__ void row_stats_from_partials(const float2 *partials, 
     float2 v[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j)
-      v[j] = g0 + j < groups ? __ldg(src + static_cast<long long>(g0 + j) * M) : make_float2(0.f, 0.f);
+      v[j] = g0 + j < groups ? __ldcg(src + static_cast<long long>(g0 + j) * M) : make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       sum += v[j].x;
@@ -178,8 +178,10 @@ __device__ __forceinline__ RowAffine epilogue_row_affine(const EpilogueParams &e
 __device__ __forceinline__ float2 epilogue_load_col_sums(const EpilogueParams &ep, int c0, int lane) {
   float2 cs = make_float2(0.f, 0.f);
   if (ep.col_sum == nullptr HOM_DIAG(|| (ep.dbg & 4096))) return cs;
-  if (c0 + lane < ep.N) cs.x = __ldg(ep.col_sum + c0 + lane);
-  if (c0 + 32 + lane < ep.N) cs.y = __ldg(ep.col_sum + c0 + 32 + lane);
+  // (L2 loads: both these sums, when B is not a declared weight, and the row statistics above
+  // were written by the kernel just before this one)
+  if (c0 + lane < ep.N) cs.x = __ldcg(ep.col_sum + c0 + lane);
+  if (c0 + 32 + lane < ep.N) cs.y = __ldcg(ep.col_sum + c0 + 32 + lane);
   return cs;
 }
 
