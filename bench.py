@@ -924,7 +924,8 @@ def run_grid_arm(args):
             weights = make_weights_torch(cfg, seq, device)
             for batch in (1, 8, 16, 32):
                 wl = dict(model=model, batch=batch, seq=seq, scaling="weak", lens=None)
-                prog = BertProgram(cfg, batch, seq)
+                prog = BertProgram(cfg, batch, seq, fused_embedding=args.fused_embedding,
+                                   fused_layernorm=args.fused_layernorm)
                 prog.set_weights(weights)
                 ids, mask, types = (torch.from_numpy(x).to(device) for x in make_inputs(wl, batch, 0))
                 for _ in range(3):
