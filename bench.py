@@ -618,18 +618,25 @@ def measure_workload(args, ranks, hom, stream, cfg, workload, name, *, full: boo
     # reported beside the headline (which stays the reference's call sequence), never as it
     if args.fused_layernorm == 0 and not args.no_extensions:
         ext = {}
-        for mode, label in ((1, "gemm_residual_layernorm_fused"), (2, "deferred_layernorm")):
-            prog_x = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding, fused_layernorm=mode)
-            prog_x.set_weights(weights)
-            for _ in range(3):
-                prog_x.forward(ids_d, mask_d, types_d, use_graph=True)
-            hom.synchronize()
-            ms_x, n_x, _ = timed_region(ranks, stream, lambda: prog_x.forward(ids_d, mask_d, types_d, use_graph=True),
-                                        steps, min_seconds=0.5)
-            hom.synchronize()
-            ext[label] = {"value": global_batch / (ms_x / 1e3), "unit": "sequences/s", "ms_per_step": ms_x,
-                          "steps_timed": n_x, "launches_per_forward": prog_x.launches_per_forward()}
-            prog_x.close()
+        try:
+            for mode, label in ((1, "gemm_residual_layernorm_fused"), (2, "deferred_layernorm")):
+                prog_x = BertProgram(cfg, local_batch, seq, fused_embedding=args.fused_embedding, fused_layernorm=mode)
+                prog_x.set_weights(weights)
+                for _ in range(3):
+                    prog_x.forward(ids_d, mask_d, types_d, use_graph=True)
+                hom.synchronize()
+                ms_x, n_x, _ = timed_region(ranks, stream,
+                                            lambda: prog_x.forward(ids_d, mask_d, types_d, use_graph=True),
+                                            steps, min_seconds=0.5)
+                hom.synchronize()
+                ext[label] = {"value": global_batch / (ms_x / 1e3), "unit": "sequences/s", "ms_per_step": ms_x,
+                              "steps_timed": n_x, "launches_per_forward": prog_x.launches_per_forward()}
+                prog_x.close()
+        except Exception as e:  # an option of the replay program must not take the headline down with it
+            if ranks.world > 1:
+                raise  # the other ranks are inside the timed region's barriers: fail the whole job instead
+            ext["error"] = f"{type(e).__name__}: {e}"
+            hom.clear_error()
         ext["note"] = ("replay-program options that change the call sequence: GEMM + residual + LayerNorm in one "
                        "cluster kernel (same rounding points as the sequence), and LayerNorm deferred into the "
                        "consumers' epilogues (no fp16 rounding of the LayerNorm output)")
